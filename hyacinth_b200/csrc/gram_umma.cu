@@ -1,0 +1,316 @@
+// Residue Gram kernel for sm_100a: int8 x int8 -> int32 on the 5th-generation tensor cores.
+//
+// Replaces, for the CRT route, the reference's cuBLAS INT8 GEMM calls plus the int32 scratch pass that
+// reduces them modulo m (src/hyacin_herk.cpp:95-109,163-189 and src/crt_diag_real.cu:13-29): the modular
+// reduction is the epilogue of the GEMM tile, so the only thing that leaves the SM is one byte per
+// (entry, modulus).
+//
+// Structure (one CTA per SM, persistent over (modulus, tile) work items):
+//   warp 0     TMA producer: 128-byte-swizzled K-major boxes of the A operand (128 Gram rows) and the B
+//              operand (256 Gram columns) into a 4-stage shared-memory ring, completion on mbarriers;
+//   warp 1     MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M128 N256 K32) on shared-memory
+//              descriptors, accumulating in one of two 256-column TMEM buffers; tcgen05.commit releases the
+//              stage and, after the last K block, hands the accumulator to the epilogue;
+//   warps 2-5  epilogue: tcgen05.ld of the int32 accumulator (32 lanes x 32 columns per load), reduction
+//              modulo m, optional accumulation onto the residues of earlier row chunks, 32-byte stores.
+// The two TMEM buffers let the epilogue of one tile overlap the main loop of the next.
+// No TMA load in this file uses cluster multicast.  Every wait is bounded: a wait that expires raises a
+// status word for the host and makes all roles leave their loops so that TMEM is still released.
+#include "hyb_internal.h"
+#include "crt_tables.h"
+#include <cuda.h>
+#include <mutex>
+
+namespace hyb {
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kUmmaK = 32;                                    // K per tcgen05.mma for 8-bit operands
+constexpr uint32_t kABytes = kTileY * kStageK;                // 16 KiB
+constexpr uint32_t kBBytes = kTileX * kStageK;                // 32 KiB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;           // 48 KiB
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr uint32_t kTmemCols = 512;                           // two accumulators of kTileX columns
+constexpr uint32_t kSpinLimit = 1u << 22;                     // bounded waits: a few seconds at most
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers*/;
+
+struct ModConsts {
+  uint32_t modulus[crt::kMaxModuli];
+  uint32_t magic[crt::kMaxModuli];      // floor(2^32 / m)
+  uint32_t bias[crt::kMaxModuli];       // multiple of m in (2^31 - m, 2^31]: makes the accumulator non-negative
+};
+
+struct GramParams {
+  uint8_t* residues; uint32_t* status;
+  int ka0, kb0;                 // first K row of the A / B operand inside a column
+  int num_kblocks;              // k_rows / kStageK
+  int num_tiles, tiles_y, moduli, accumulate;
+  ModConsts k;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the wait expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t* status, uint32_t code) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) { if (*abort_flag) return false; __nanosleep(it > 4096 ? 256 : 32); }
+  }
+  *abort_flag = 1u;
+  *reinterpret_cast<volatile uint32_t*>(status) = code;      // plain store: the word lives in mapped host memory
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte
+// swizzle: groups of 8 rows (1024 bytes) follow each other, so the stride byte offset is 1024.
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+  d |= uint64_t(1) << 16;                          // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t(1024 >> 4) << 32;                  // stride byte offset
+  d |= uint64_t(1) << 46;                          // descriptor version of sm_100
+  d |= uint64_t(2) << 61;                          // SWIZZLE_128B
+  return d;
+}
+// kind::i8 instruction descriptor: s8 x s8 -> s32, both operands K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(kTileX >> 3) << 17) | (uint32_t(kTileY >> 4) << 24);
+
+struct Barriers {
+  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base; uint32_t abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                 // swizzle atoms need 1 KiB alignment
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  Barriers* bars = reinterpret_cast<Barriers*>(aligned + size_t(kStages) * kStageBytes);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_items = p.moduli * p.num_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&bars->acc_full[a], 1); mbar_init(&bars->acc_empty[a], kEpilogueWarps); }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&bars->tmem_base, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0; bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int m = item / p.num_tiles; int ty, tx; tile_coords(p.tiles_y, item % p.num_tiles, &ty, &tx);
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 1u))) break;
+          mbar_expect_tx(&bars->full[stage], kStageBytes);
+          const uint32_t sa = base + stage * kStageBytes, sb = sa + kABytes;
+          tma_load_3d(sa, &tmap, &bars->full[stage], p.ka0 + kb * kStageK, ty * kTileY, m);
+          tma_load_3d(sb, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX, m);
+          tma_load_3d(sb + kABytes, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX + kTileY, m);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0; bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        if (!(ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2u))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileX;
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->full[stage], phase, abort_flag, p.status, 3u))) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * kStageBytes, sb = sa + kABytes;
+          const uint64_t adesc = smem_desc_k128(sa), bdesc = smem_desc_k128(sb);
+#pragma unroll
+          for (int k = 0; k < kStageK / kUmmaK; ++k) {
+            // advancing K inside the swizzle row: +32 bytes = +2 in 16-byte units of the start-address field
+            umma_i8(tmem_d, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->empty[stage]);              // frees the stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&bars->acc_full[acc]);               // accumulator complete -> epilogue
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps ----------------
+    const int lane_group = warp & 3;                     // TMEM lanes 32 * (warp % 4) .. +31 are visible to this warp
+    const int row = lane_group * 32 + lane;
+    uint32_t acc = 0, acc_phase = 0; bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int m = item / p.num_tiles, tile = item % p.num_tiles;
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status, 4u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t modulus = p.k.modulus[m], magic = p.k.magic[m], bias = p.k.bias[m];
+      uint8_t* out = p.residues + (size_t(m) * p.num_tiles + tile) * size_t(kTileY * kTileX) + size_t(row) * kTileX;
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
+#pragma unroll 1
+      for (int c = 0; c < kTileX / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        uint4 old0 = make_uint4(0, 0, 0, 0), old1 = old0;
+        if (p.accumulate) { old0 = *reinterpret_cast<const uint4*>(out + c * 32); old1 = *reinterpret_cast<const uint4*>(out + c * 32 + 16); }
+        tmem_ld_wait();
+        const uint32_t oldw[8] = {old0.x, old0.y, old0.z, old0.w, old1.x, old1.y, old1.z, old1.w};
+        uint32_t packed[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            // accumulator + bias is non-negative and congruent to the accumulator; add the previous residue,
+            // estimate the quotient (at most one too small), correct once.
+            uint32_t t = v[w * 4 + b] + bias + ((oldw[w] >> (8 * b)) & 0xFFu);
+            uint32_t r = t - __umulhi(t, magic) * modulus;
+            r = r >= modulus ? r - modulus : r;
+            word |= r << (8 * b);
+          }
+          packed[w] = word;
+        }
+        *reinterpret_cast<uint4*>(out + c * 32) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(out + c * 32 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // Teardown: every role ends up here, also after an expired wait, so TMEM is always released.
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// ---- host side ------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr; cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else std::fprintf(stderr, "hyacin-b200: cuTensorMapEncodeTiled is not available from this driver\n");
+  });
+  return fn;
+}
+
+}  // namespace
+
+TilePlan make_tile_plan(int n) {
+  TilePlan t; t.n = n;
+  t.tiles_x = (n + kTileX - 1) / kTileX; t.tiles_y = (n + kTileY - 1) / kTileY;
+  int count = 0;
+  for (int x = 0; x < t.tiles_x; ++x) { int c = 2 * x + 2; count += c < t.tiles_y ? c : t.tiles_y; }
+  t.num_tiles = count;
+  return t;
+}
+
+void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return;
+  const TilePlan tp = make_tile_plan(g.n);
+  CUtensorMap tmap;
+  const cuuint64_t dims[3] = {cuuint64_t(g.ldw), cuuint64_t(g.n), cuuint64_t(g.moduli)};
+  const cuuint64_t strides[2] = {cuuint64_t(g.ldw), cuuint64_t(g.plane_stride)};
+  const cuuint32_t box[3] = {cuuint32_t(kStageK), cuuint32_t(kTileY), 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(g.w), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { std::fprintf(stderr, "hyacin-b200: cuTensorMapEncodeTiled failed (%d)\n", int(r)); return; }
+
+  GramParams p;
+  p.residues = g.residues; p.status = g.status;
+  p.ka0 = g.ka0; p.kb0 = g.kb0; p.num_kblocks = g.k_rows / kStageK;
+  p.num_tiles = tp.num_tiles; p.tiles_y = tp.tiles_y; p.moduli = g.moduli; p.accumulate = g.accumulate;
+  for (int i = 0; i < crt::kMaxModuli; ++i) {
+    const uint32_t m = crt::kModulus[i];
+    p.k.modulus[i] = m; p.k.magic[i] = crt::kMagicFloor[i];
+    p.k.bias[i] = (0x80000000u / m) * m;
+  }
+  HYB_CUDA(cudaFuncSetAttribute(gram_residue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+  const int items = g.moduli * tp.num_tiles;
+  int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > items) grid = items;
+  if (grid <= 0 || p.num_kblocks <= 0) return;
+  gram_residue_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+  HYB_CUDA(cudaGetLastError());
+}
+
+}  // namespace hyb

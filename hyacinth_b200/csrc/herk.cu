@@ -1,0 +1,224 @@
+// Host orchestration of the quantized Gram: sizing, column exponents, the integer HERK and dequantisation.
+//
+// Entry points keep the reference's names, arguments and no-op rules (src/hyacin_herk.cpp:45-59, 386-407;
+// src/fp_exponent.cu:53-65; src/fp_i63tp_dequantize.cu:29-54, 143-159).  The schedule behind
+// hyacinXherkBatch is new.  The reference buckets row segments into a precision ladder, flushes the CRT
+// accumulation every 8192 rows through cuBLAS GEMMs into an int32 scratch and reconstructs after every
+// flush.  Here every row goes through one CRT pipeline sized for the whole call:
+//     for each row chunk (<= 65536 rows):  quantize -> residue Gram (tcgen05), residues accumulate mod m
+//     once per call (or per 2^k-row group when the bit budget demands it): Garner reconstruction into C
+// The integer Gram C = sum_k q_ky q_kx is exact under either schedule, so results are bit-identical.
+#include "hyb_internal.h"
+#include "crt_tables.h"
+#include <hyacin_b200.h>
+#include <algorithm>
+#include <climits>
+#include <cmath>
+
+namespace hyb {
+
+static int ceil_log2_u64(uint64_t v) { int l = 0; while (l < 64 && (uint64_t(1) << l) < v) ++l; return l; }
+
+CrtPlan make_crt_plan(int u, int cplx, int64_t rows) {
+  CrtPlan p{}; if (u < 0 || rows <= 0) return p;
+  p.value_bytes = (u + 9) / 8;                       // |q| <= 2^u must stay below the bias 2^(8 nb - 1)
+  auto bits_for = [&](int64_t g) { return 2 * u + 1 + cplx + ceil_log2_u64(uint64_t(g)); };
+  int64_t group = rows;
+  const int max_bits = crt::kRangeBits[crt::kMaxModuli - 1];
+  if (bits_for(group) > max_bits) { group = 1; while (group * 2 <= rows && bits_for(group * 2) <= max_bits) group *= 2; }
+  if (group > (int64_t(1) << 30)) group = int64_t(1) << 30;
+  const int need = bits_for(group);
+  int k = 1; while (k < crt::kMaxModuli && crt::kRangeBits[k - 1] < need) ++k;
+  p.moduli = k; p.group_rows = int(group);
+  // Rows per kernel launch: bounded by the int32 accumulator (a complex operand stacks two parts along K)
+  // and by a ~4 GiB residue-plane workspace.
+  int64_t chunk = cplx ? 32768 : 65536;
+  p.chunk_rows = int(std::min<int64_t>(chunk, (group + kStageK - 1) / kStageK * kStageK));
+  return p;
+}
+
+// ---- status word shared with the kernels (pinned, mapped; written by a kernel only when a wait expires) ----
+static uint32_t* g_status_host[64] = {};
+static uint32_t* g_status_dev[64] = {};
+uint32_t* status_word_device(int device) {
+  if (device < 0 || device >= 64) return nullptr;
+  if (!g_status_host[device]) {
+    uint32_t* h = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped) != cudaSuccess) return nullptr;
+    *h = 0;
+    void* d = nullptr; if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) { cudaFreeHost(h); return nullptr; }
+    g_status_host[device] = h; g_status_dev[device] = static_cast<uint32_t*>(d);
+  }
+  return g_status_dev[device];
+}
+uint32_t status_word_read(int device, bool clear) {
+  if (device < 0 || device >= 64 || !g_status_host[device]) return 0;
+  volatile uint32_t* p = g_status_host[device]; uint32_t v = *p; if (clear) *p = 0; return v;
+}
+void status_check(const hyacinHandle_t* handle, const char* where) {
+  uint32_t v = status_word_read(handle->DeviceID, false);
+  if (v) std::fprintf(stderr, "hyacin-b200: ERROR: a bounded wait inside the Gram kernel expired (code %u), seen at %s; "
+                              "the integer Gram of that call is invalid\n", v, where);
+}
+
+static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda,
+                     int u, const int32_t* vexp, int beta, int order, uint64_t* C) {
+  cudaStream_t stream = handle->cudaStream;
+  const int cplx = is_complex(atype), parts = cplx ? 3 : 1;
+  const int64_t tri = (int64_t(n) * n + n) / 2;
+  const CrtPlan plan = make_crt_plan(u, cplx, rows);
+  if (plan.moduli == 0) return;
+  const TilePlan tp = make_tile_plan(n);
+  const size_t elem = (base_type(atype) == HYACIN_F64 ? 8 : base_type(atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);
+  const size_t w_bytes = size_t(plan.chunk_rows) * parts * size_t(n) * plan.moduli;
+  const size_t r_bytes = size_t(plan.moduli) * tp.num_tiles * size_t(kTileY) * kTileX;
+  int8_t* W = nullptr; uint8_t* R = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&W), w_bytes, handle->mempool, stream));
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&R), r_bytes * (cplx ? 2 : 1), handle->mempool, stream));
+  uint32_t* status = status_word_device(handle->DeviceID);
+  if (!W || !R || !status) { if (W) cudaFreeAsync(W, stream); if (R) cudaFreeAsync(R, stream); return; }
+
+  for (int64_t row = 0; row < rows; row += plan.group_rows) {
+    const int64_t g = std::min<int64_t>(plan.group_rows, rows - row);
+    bool first = true;
+    for (int64_t c0 = 0; c0 < g; c0 += plan.chunk_rows) {
+      const int rc = int(std::min<int64_t>(plan.chunk_rows, g - c0));
+      const int64_t ldk = (rc + kStageK - 1) / kStageK * kStageK;
+      const char* src = static_cast<const char*>(A) + size_t(row + c0) * elem;
+      launch_quantize_crt(stream, atype, rc, n, src, lda, vexp, plan, W, ldk);
+      GramLaunch gl{};
+      gl.w = W; gl.ldw = ldk * parts; gl.plane_stride = gl.ldw * n;
+      gl.ka0 = 0; gl.kb0 = 0; gl.k_rows = int(ldk) * (cplx ? 2 : 1); gl.n = n; gl.moduli = plan.moduli;
+      gl.accumulate = first ? 0 : 1; gl.sm_count = handle->DeviceSMs; gl.residues = R; gl.status = status;
+      launch_gram_residues(stream, gl);               // real part: (re; im)^T (re; im)
+      if (cplx) { gl.kb0 = int(ldk); gl.residues = R + r_bytes; launch_gram_residues(stream, gl); }   // (re; im)^T (im; -re)
+      first = false;
+    }
+    launch_reconstruct(stream, n, plan.moduli, R, beta, order, C);
+    if (cplx) launch_reconstruct(stream, n, plan.moduli, R + r_bytes, beta, order, C + size_t(order) * tri);
+    beta = 1;
+  }
+  HYB_CUDA(cudaFreeAsync(W, stream));
+  HYB_CUDA(cudaFreeAsync(R, stream));
+  if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "I8I32-GEMM-%s [algo=TN,crt,tcgen05] [M=N=%d] [K=%lld] [Order=%d]\n",
+                                   cplx ? "COMPLEX" : "REAL", n, (long long)rows, plan.moduli);
+}
+
+}  // namespace hyb
+
+extern "C" void hyacinXherkBatchInit(const hyacinHandle_t* handle, double eps, uint64_t M, int32_t N, hyacinPrecision_t Atype,
+                                     int32_t* uA, int32_t* cPanels, int32_t* lPanels, uint64_t* stride) {
+  if (stride) { const uint64_t n = uint64_t(std::max(0, N)); *stride = (n * n + n) >> 1; }
+  if (!uA && !cPanels && !lPanels) return;
+  if (int(Atype) < 0 || int(Atype) > 11) return;
+  static const int mantissa[12] = {52, 52, 23, 23, 10, 10, 105, 105, 71, 71, 95, 95};
+  const int log2m = M > 1 ? hyb::ceil_log2_u64(M) : 0;       // log2 of the row count rounded up to a power of two
+  int e = 0; const double f = std::frexp(std::fabs(eps), &e);
+  const int u = std::min(std::max((f == 0.5 ? 1 : 0) - e, 0), mantissa[int(Atype)]);
+  const int cplx = hyb::is_complex(Atype);
+  const int u_corr = std::max(-1, std::min(80, handle->QuantizeBitCorrection + u));
+  if (uA) *uA = u_corr;
+  if (cPanels) *cPanels = 1 + cplx;
+  if (lPanels) *lPanels = u_corr >= 0 ? (63 + std::max(0, 2 * (u_corr + cplx)) + log2m) / 63 : 0;
+}
+
+extern "C" void hyacinXquantizeScaleBatch(const hyacinHandle_t* handle, int32_t batches, int32_t segM, int32_t lastM, int32_t N,
+                                          hyacinPrecision_t Atype, const void* A, int32_t lda, int32_t uA, int32_t* vexp) {
+  if (N <= 0 || int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX)) return;
+  hyb::timer_mark(handle, hyb::Segment::Distributed);
+  hyb::launch_column_exponents(handle->cudaStream, Atype, batches, segM, lastM, N, A, lda, uA, vexp);
+}
+
+extern "C" void hyacinXherkBatch(const hyacinHandle_t* handle, int32_t batches, int32_t segM, int32_t lastM, int32_t N,
+                                 hyacinPrecision_t Atype, const void* A, int32_t lda, int32_t u, const int32_t* vexp,
+                                 int32_t beta, int32_t orderC, uint64_t* C) {
+  if (N <= 0 || orderC <= 0 || orderC > 3) return;
+  if (int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX)) return;
+  hyb::timer_mark(handle, hyb::Segment::Distributed);
+  const int64_t rows = batches <= 1 ? int64_t(lastM) : int64_t(batches - 1) * segM + lastM;
+  const int cplx = hyb::is_complex(Atype);
+  if (rows <= 0 || u < 0) {
+    // Nothing to add: an overwrite still has to define C (src/hyacin_herk.cpp:287).
+    if (beta == 0) {
+      const uint64_t tri = (uint64_t(N) * N + N) / 2;
+      HYB_CUDA(cudaMemsetAsync(C, 0, tri * uint64_t(orderC) * (1 + cplx) * sizeof(uint64_t), handle->cudaStream));
+    }
+    return;
+  }
+  hyb::herk_crt(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
+}
+
+extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
+                                      hyacinPrecision_t Atype, hyacinPrecision_t* Gtype, int32_t* gElemBytes) {
+  if (N <= 0 && (Gtype != nullptr || gElemBytes != nullptr)) return;
+  if (int(Atype) < 0 || int(Atype) > 11) return;
+  hyb::timer_mark(handle, hyb::Segment::Replicated);
+  int32_t* bits_host = static_cast<int32_t*>(handle->pinnedWorkspace);
+  *bits_host = 0;
+  hyb::launch_gram_range(handle->cudaStream, N, orderC, C, vexp, bits_host);
+  HYB_CUDA(cudaStreamSynchronize(handle->cudaStream));
+  hyb::status_check(handle, "hyacinXdequantizeInit");
+  static const int bytes[12] = {8, 16, 4, 8, 2, 4, 16, 32, 12, 24, 16, 32};
+  const int bits = *bits_host - 2 * handle->QuantizeBitCorrection;
+  const bool wide_fp64 = handle->DeviceIsF64Capable != 0;
+  hyacinPrecision_t g = bits <= 23 ? HYACIN_F32_COMPLEX
+                      : bits <= 52 ? HYACIN_F64_COMPLEX
+                      : (bits <= 71 && !wide_fp64) ? HYACIN_TF_COMPLEX
+                      : (bits <= 95 && !wide_fp64) ? HYACIN_QF_COMPLEX : HYACIN_DD_COMPLEX;
+  if (!hyb::is_complex(Atype)) g = hyacinPrecision_t(int(g) - 1);
+  if (Gtype) *Gtype = g;
+  if (gElemBytes) *gElemBytes = bytes[int(g)];
+}
+
+extern "C" void hyacinXdequantize(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
+                                  hyacinPrecision_t Gtype, void* G, int32_t ldg) {
+  if (N <= 0) return;
+  hyb::timer_mark(handle, hyb::Segment::Replicated);
+  hyb::launch_dequantize(handle->cudaStream, N, orderC, C, vexp, Gtype, G, ldg);
+}
+
+// ---- stage-level entry points of this build (declared in hyacin_b200.h) ---------------------------------
+extern "C" uint32_t hyacinB200Status(int32_t clear) {
+  int dev = 0; if (cudaGetDevice(&dev) != cudaSuccess) return 0xFFFFFFFFu;
+  return hyb::status_word_read(dev, clear != 0);
+}
+
+extern "C" void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int32_t* moduli, int32_t* valueBytes,
+                                  int32_t* groupRows, int32_t* chunkRows) {
+  const hyb::CrtPlan p = hyb::make_crt_plan(u, Complex ? 1 : 0, rows);
+  if (moduli) *moduli = p.moduli; if (valueBytes) *valueBytes = p.value_bytes;
+  if (groupRows) *groupRows = p.group_rows; if (chunkRows) *chunkRows = p.chunk_rows;
+}
+
+extern "C" void hyacinB200TileInfo(int32_t N, int32_t* tileY, int32_t* tileX, int32_t* tilesY, int32_t* numTiles) {
+  const hyb::TilePlan tp = hyb::make_tile_plan(N);
+  if (tileY) *tileY = hyb::kTileY; if (tileX) *tileX = hyb::kTileX;
+  if (tilesY) *tilesY = tp.tiles_y; if (numTiles) *numTiles = tp.num_tiles;
+}
+
+extern "C" void hyacinB200QuantizeCrt(const hyacinHandle_t* handle, hyacinPrecision_t Atype, int32_t rows, int32_t N, const void* A,
+                                      int32_t lda, const int32_t* vexp, int32_t moduli, int32_t valueBytes, int8_t* W, int64_t ldk) {
+  if (N <= 0 || rows < 0 || moduli <= 0 || moduli > hyb::crt::kMaxModuli || valueBytes < 1 || valueBytes > hyb::crt::kMaxBytes) return;
+  if (int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX) || ldk % hyb::kStageK) return;
+  hyb::CrtPlan p{}; p.moduli = moduli; p.value_bytes = valueBytes;
+  hyb::launch_quantize_crt(handle->cudaStream, Atype, rows, N, A, lda, vexp, p, W, ldk);
+}
+
+extern "C" void hyacinB200GramResidues(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const int8_t* W, int64_t ldw,
+                                       int64_t planeStride, int32_t ka0, int32_t kb0, int32_t kRows, int32_t accumulate,
+                                       uint8_t* residues) {
+  if (N <= 0 || moduli <= 0 || moduli > hyb::crt::kMaxModuli || kRows <= 0) return;
+  if (kRows % hyb::kStageK || ka0 % hyb::kStageK || kb0 % hyb::kStageK || ldw % 16 || planeStride % 16 || kRows > hyb::kMaxAccumRows) return;
+  hyb::GramLaunch g{};
+  g.w = W; g.ldw = ldw; g.plane_stride = planeStride; g.ka0 = ka0; g.kb0 = kb0; g.k_rows = kRows; g.n = N; g.moduli = moduli;
+  g.accumulate = accumulate ? 1 : 0; g.sm_count = handle->DeviceSMs; g.residues = residues;
+  g.status = hyb::status_word_device(handle->DeviceID);
+  if (!g.status) return;
+  hyb::launch_gram_residues(handle->cudaStream, g);
+}
+
+extern "C" void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const uint8_t* residues, int32_t beta,
+                                      int32_t orderC, uint64_t* Cpanel) {
+  if (N <= 0 || moduli <= 0 || moduli > hyb::crt::kMaxModuli || orderC <= 0 || orderC > 3) return;
+  hyb::launch_reconstruct(handle->cudaStream, N, moduli, residues, beta ? 1 : 0, orderC, Cpanel);
+}

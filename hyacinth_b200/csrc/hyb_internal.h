@@ -1,0 +1,115 @@
+// Internal interfaces of the B200 Hyacin build (host side).  Nothing here is part of the public ABI.
+#pragma once
+#include <hyacin.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+
+namespace hyb {
+
+// ---------------------------------------------------------------------------------------------------
+// Error reporting.  The public ABI has no error channel (the reference drops CUDA errors in release
+// builds); this build keeps going as well but says so on stderr, once per call site.
+// ---------------------------------------------------------------------------------------------------
+void report_cuda_error(cudaError_t err, const char* what, const char* file, int line);
+#define HYB_CUDA(call) do { cudaError_t hyb_err_ = (call); if (hyb_err_ != cudaSuccess) \
+  ::hyb::report_cuda_error(hyb_err_, #call, __FILE__, __LINE__); } while (0)
+
+inline int is_complex(hyacinPrecision_t t) { return int(t) & 1; }
+inline int base_type(hyacinPrecision_t t) { return int(t) & ~1; }
+
+// Status word of the bounded waits in the Gram kernel (pinned host memory mapped into the device).
+uint32_t* status_word_device(int device);
+uint32_t status_word_read(int device, bool clear);
+void status_check(const hyacinHandle_t* handle, const char* where);
+
+// Timer classes of hyacinSync_TimerSegments ('D', 'R', 'C'; anything else untimed).
+enum class Segment : unsigned char { Untimed, Distributed, Replicated, Comm };
+void timer_mark(const hyacinHandle_t* handle, Segment seg);
+
+// ---------------------------------------------------------------------------------------------------
+// Geometry of the residue Gram kernel.
+//   One work item = one (modulus, tile) pair; a tile is kTileY rows (y, the A operand) by kTileX columns
+//   (x, the B operand) of the Gram matrix, kept only if it intersects the upper triangle y <= x.
+//   Residues of a tile are stored as kTileY x kTileX bytes, x fastest, tiles in the order of tile_list().
+// ---------------------------------------------------------------------------------------------------
+constexpr int kTileY = 128;
+constexpr int kTileX = 256;
+constexpr int kStageK = 128;                       // bytes of K per pipeline stage (one 128-byte swizzle row)
+constexpr int kMaxAccumRows = 130816;              // 128 * 128 * rows < 2^31 keeps the int32 accumulator exact
+
+struct TilePlan {
+  int n;            // Gram dimension
+  int tiles_x;      // ceil(n / kTileX)
+  int tiles_y;      // ceil(n / kTileY)
+  int num_tiles;    // tiles that touch the upper triangle
+};
+TilePlan make_tile_plan(int n);
+// Linear tile index -> (ty, tx).  Column-block major: all ty of tx = 0, then tx = 1, ...
+__host__ __device__ inline void tile_coords(int n_tiles_y, int t, int* ty, int* tx) {
+  // Tiles of column block tx: ty = 0 .. min(tiles_y, 2 tx + 2) - 1  (kTileX == 2 kTileY).
+  int x = 0, base = 0;
+  for (;;) {
+    int cnt = 2 * x + 2; if (cnt > n_tiles_y) cnt = n_tiles_y;
+    if (t < base + cnt) { *ty = t - base; *tx = x; return; }
+    base += cnt; ++x;
+  }
+}
+
+// Plan of one hyacinXherkBatch call: how many moduli, how rows are grouped and chunked.
+struct CrtPlan {
+  int moduli;          // number of CRT moduli (prefix of crt::kModulus)
+  int value_bytes;     // bytes needed for a biased quantised value (1..12)
+  int group_rows;      // rows reconstructed together (residues accumulate across the chunks of a group)
+  int chunk_rows;      // rows quantised and multiplied per kernel launch (multiple of kStageK)
+};
+// u: quantisation bits of the call; cplx: 0/1; rows: rows of this call.  Returns moduli == 0 if impossible.
+CrtPlan make_crt_plan(int u, int cplx, int64_t rows);
+
+// ---------------------------------------------------------------------------------------------------
+// Kernel launchers (all asynchronous on `stream`).
+// ---------------------------------------------------------------------------------------------------
+
+// Column exponents: fills vexp[(batches+1) x N].  Reference behaviour: src/fp_exponent.cu:45-51.
+void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int batches, int seg_m, int last_m, int n,
+                             const void* A, int64_t lda, int u, int32_t* vexp);
+// Bits needed per row segment (segU[batches]).  Reference behaviour: src/fp_exponent.cu:67-76.
+void launch_vector_range(cudaStream_t stream, int batches, int n, int u, const int32_t* vexp, int32_t* seg_u);
+
+// Quantise rows [0, rows) of A (column-major, 'N' orientation) into centred int8 residue planes
+//   W[modulus][column][part * ldk + row]     (ldk a multiple of kStageK; rows in [rows, ldk) are zeroed)
+// Real input has one part.  Complex input has three, stacked along K inside each column: real, imaginary,
+// negated real -- so that rows [0, 2 ldk) are the operand (re; im) and rows [ldk, 3 ldk) the operand (im; -re).
+void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
+                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk);
+
+// Residue Gram of one chunk.  For every modulus m and every upper-triangle tile:
+//   R[m][tile][y][x] = (accumulate ? R : 0) + sum_{k < k_rows} W[m][y][ka0 + k] * W[m][x][kb0 + k]  (mod m), a byte.
+// W has column pitch ldw and plane pitch plane_stride (bytes); k_rows, ka0, kb0 are multiples of kStageK.
+// status: device word that becomes non-zero if a bounded wait inside the kernel expired.
+struct GramLaunch {
+  const int8_t* w;
+  int64_t ldw, plane_stride;
+  int ka0, kb0, k_rows, n, moduli, accumulate, sm_count;
+  uint8_t* residues;            // [moduli][num_tiles][kTileY * kTileX]
+  uint32_t* status;
+};
+void launch_gram_residues(cudaStream_t stream, const GramLaunch& g);
+
+// CRT reconstruction of `moduli` residue planes into the packed 63-bit-limb Gram:
+//   C[panel][order][tri] = (beta ? C : 0) + value.  Reference counterpart: src/crt_reconstruct_real.cu:51-92.
+void launch_reconstruct(cudaStream_t stream, int n, int moduli, const uint8_t* residues, int beta, int order,
+                        uint64_t* C_panel);
+
+// Largest bit length among the true-scale diagonal entries (written to *bits_out, device or pinned).
+void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, int32_t* bits_out);
+// Packed integer Gram -> full Hermitian floating-point matrix.
+void launch_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp,
+                       hyacinPrecision_t gtype, void* G, int64_t ldg);
+
+// Slices for the cross-rank sum: A[panels][order][count] -> S[panels][slice_count][count] and back.
+int slice_count(int order, int ranks);
+void launch_limbs_to_slices(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* A, uint64_t* S);
+void launch_slices_to_limbs(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* S, uint64_t* A);
+
+}  // namespace hyb

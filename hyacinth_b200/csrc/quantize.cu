@@ -1,0 +1,150 @@
+// Quantiser: floating-point rows of A -> centred int8 CRT residue planes, the operands of the Gram kernel.
+//
+// Contract (reference: src/quantize_limbs.cu:14-18 for the rounding, src/quantize_crt_real.cu:30-34,63-67 and
+// src/quantize_crt_complex.cu:30-42 for the residue planes): q = rint_ties_even(a * 2^vexp[col]); each plane
+// holds q mod m as an int8.  Any representative in [-128, 127] is admissible -- the Gram of residues is only
+// ever used modulo m -- so this kernel stores ((q + 128) mod m) - 128.
+//
+// How the residue is formed (new): q is biased by 2^(8 nb - 1) so that its nb bytes are unsigned; then
+//   q + 128 = bias_m + sum_b byte_b * (256^b mod m)   (mod m)
+// is one dp4a per four bytes, and the sum (< 2^20) is reduced with a single exact multiply-high.
+// Each thread converts four consecutive rows of one column and stores one 32-bit word per plane, so loads
+// and stores of a warp are contiguous 1 KiB / 128 B runs.
+#include "hyb_internal.h"
+#include "crt_tables.h"
+#include <cuda_fp16.h>
+#include <climits>
+
+namespace hyb {
+namespace {
+
+struct QuantConsts {
+  uint32_t modulus[crt::kMaxModuli];
+  uint32_t magic[crt::kMaxModuli];          // ceil(2^32 / m)
+  uint32_t bias[crt::kMaxModuli];           // (128 - 2^(8 nb - 1)) mod m
+  uint32_t weight[crt::kMaxModuli][3];      // 256^b mod m, four per word
+};
+
+struct QuantParams {
+  const void* A; int64_t lda;               // elements
+  const int32_t* vexp;
+  int8_t* W; int64_t col_pitch, plane_pitch, part_pitch;   // bytes; part_pitch = rows per part (ldk)
+  int rows, ldk, n, moduli, value_bytes;
+  QuantConsts k;                            // kernel parameters live in the constant bank
+};
+
+template <typename T> __device__ __forceinline__ double load_as_double(const T* p);
+template <> __device__ __forceinline__ double load_as_double<double>(const double* p) { return *p; }
+template <> __device__ __forceinline__ double load_as_double<float>(const float* p) {
+  float f = *p;
+  // Single-precision subnormals count as zero, as in a flush-to-zero (fast-math) build of the reference.
+  return fabsf(f) < 1.17549435e-38f ? 0.0 : double(f);
+}
+template <> __device__ __forceinline__ double load_as_double<__half>(const __half* p) { return double(__half2float(*p)); }
+
+__device__ __forceinline__ double pow2(int e) { return __longlong_as_double((long long)(e + 1023) << 52); }
+
+// Residue words of one biased value (up to three 32-bit words of bytes) for modulus i, in [0, m).
+template <int NW>
+__device__ __forceinline__ uint32_t residue(const QuantConsts& k, const uint32_t (&w)[3], int i) {
+  uint32_t t = k.bias[i];
+  t = __dp4a(w[0], k.weight[i][0], t);
+  if (NW > 1) t = __dp4a(w[1], k.weight[i][1], t);
+  if (NW > 2) t = __dp4a(w[2], k.weight[i][2], t);
+  return t - __umulhi(t, k.magic[i]) * k.modulus[i];
+}
+
+// rint(v) biased by 2^(8 nb - 1), as little-endian 32-bit words.  |v| <= 2^80.
+template <int NW>
+__device__ __forceinline__ void biased_words(double v, int value_bytes, bool negate, uint32_t (&w)[3]) {
+  if (NW <= 2) {
+    long long q = __double2ll_rn(v);                      // ties to even; |v| < 2^63 on this path
+    if (negate) q = -q;
+    unsigned long long b = (unsigned long long)q + (1ull << (8 * value_bytes - 1));
+    w[0] = uint32_t(b); w[1] = uint32_t(b >> 32); w[2] = 0;
+  } else {
+    __int128 q;
+    if (fabs(v) < 4611686018427387904.0) q = __double2ll_rn(v);
+    else {                                                // already an integer: split exactly at 2^32
+      double hi = trunc(v * 2.3283064365386963e-10), lo = v - hi * 4294967296.0;
+      q = ((__int128)__double2ll_rn(hi) << 32) + (__int128)__double2ll_rn(lo);
+    }
+    if (negate) q = -q;
+    unsigned __int128 b = (unsigned __int128)q + ((unsigned __int128)1 << (8 * value_bytes - 1));
+    w[0] = uint32_t(b); w[1] = uint32_t(b >> 32); w[2] = uint32_t(b >> 64);
+  }
+}
+
+// grid.x covers ldk / (4 * blockDim.x) row groups, grid.y = columns.
+// PARTS = 1: real input.  PARTS = 3: complex input -> planes (re, im, -re) stacked along K in each column.
+template <typename T, int NW, int PARTS>
+__global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
+  const int col = blockIdx.y;
+  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (row0 >= p.ldk) return;
+  const int expon = p.vexp[col];
+  // a * 2^expon as two exact scalings: the halves stay representable for every admissible exponent, and a
+  // product that leaves the normal range on the way is far below 1/2 at the end, i.e. rounds to zero anyway.
+  double s1 = 0.0, s2 = 0.0;
+  if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+  constexpr int kReal = PARTS == 1 ? 1 : 2;
+  const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0) * kReal;
+  double v[4][kReal];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < kReal; ++c)
+      v[r][c] = (row0 + r < p.rows) ? (load_as_double<T>(src + r * kReal + c) * s1) * s2 : 0.0;
+
+  int8_t* dst = p.W + int64_t(col) * p.col_pitch + row0;
+#pragma unroll
+  for (int part = 0; part < PARTS; ++part) {
+    uint32_t w[4][3];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) biased_words<NW>(v[r][part == 1 ? 1 : 0], p.value_bytes, part == 2, w[r]);
+    int8_t* out = dst + int64_t(part) * p.part_pitch;
+#pragma unroll 1
+    for (int i = 0; i < p.moduli; ++i) {
+      uint32_t packed = residue<NW>(p.k, w[0], i) | (residue<NW>(p.k, w[1], i) << 8) |
+                        (residue<NW>(p.k, w[2], i) << 16) | (residue<NW>(p.k, w[3], i) << 24);
+      *reinterpret_cast<uint32_t*>(out + int64_t(i) * p.plane_pitch) = packed ^ 0x80808080u;   // subtract 128 per byte
+    }
+  }
+}
+
+template <typename T, int PARTS>
+void launch_typed(cudaStream_t stream, const QuantParams& p) {
+  dim3 grid(unsigned((p.ldk / 4 + 255) / 256), unsigned(p.n));
+  const int nw = (p.value_bytes + 3) / 4;
+  if (nw <= 1) quantize_crt_kernel<T, 1, PARTS><<<grid, 256, 0, stream>>>(p);
+  else if (nw == 2) quantize_crt_kernel<T, 2, PARTS><<<grid, 256, 0, stream>>>(p);
+  else quantize_crt_kernel<T, 3, PARTS><<<grid, 256, 0, stream>>>(p);
+}
+
+}  // namespace
+
+void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
+                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk) {
+  const int cplx = is_complex(atype);
+  QuantParams p;
+  for (int i = 0; i < crt::kMaxModuli; ++i) {   // the bias depends on the byte width of the values
+    p.k.modulus[i] = crt::kModulus[i]; p.k.magic[i] = crt::kMagicCeil[i];
+    p.k.bias[i] = crt::kPow2Bias[i][plan.value_bytes - 1];
+    for (int w = 0; w < 3; ++w) p.k.weight[i][w] = crt::kByteWeight[i][w];
+  }
+  p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;
+  p.part_pitch = ldk; p.col_pitch = ldk * (cplx ? 3 : 1); p.plane_pitch = p.col_pitch * n;
+  p.rows = rows; p.ldk = int(ldk); p.n = n; p.moduli = plan.moduli; p.value_bytes = plan.value_bytes;
+  switch (int(atype)) {
+    case HYACIN_F64: launch_typed<double, 1>(stream, p); break;
+    case HYACIN_F32: launch_typed<float, 1>(stream, p); break;
+    case HYACIN_F16: launch_typed<__half, 1>(stream, p); break;
+    case HYACIN_F64_COMPLEX: launch_typed<double, 3>(stream, p); break;
+    case HYACIN_F32_COMPLEX: launch_typed<float, 3>(stream, p); break;
+    case HYACIN_F16_COMPLEX: launch_typed<__half, 3>(stream, p); break;
+    default: break;
+  }
+  HYB_CUDA(cudaGetLastError());
+}
+
+}  // namespace hyb

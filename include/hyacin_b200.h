@@ -1,0 +1,57 @@
+/*
+ * hyacin_b200.h -- entry points that exist only in the B200-native build.
+ *
+ * None of them has a counterpart in the reference library; applications that stay within hyacin.h never
+ * need this header.  They expose the individual kernels of the quantized-Gram path (so that each stage can
+ * be checked in isolation) and the status word of the bounded waits inside the tensor-core kernel.
+ * Pointers are device pointers unless stated otherwise; work is enqueued on handle->cudaStream.
+ */
+#ifndef HYACIN_B200_H_
+#define HYACIN_B200_H_
+
+#include <hyacin.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Non-zero if a bounded wait inside the Gram kernel expired on the current device since the word was last
+ * cleared (the integer Gram of that call is then invalid).  Call after synchronising the stream.
+ * No counterpart in the reference (its kernels have no waits). */
+uint32_t hyacinB200Status(int32_t clear);
+
+/* Schedule of one hyacinXherkBatch call with `rows` local rows and quantisation bits u: number of CRT
+ * moduli, bytes per biased quantised value, rows reconstructed together, rows per kernel launch.
+ * Takes over the role of the reference's cost model (src/hyacin_herk.cpp:11-43) for this build. */
+void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int32_t* moduli, int32_t* valueBytes,
+                       int32_t* groupRows, int32_t* chunkRows);
+
+/* Tile geometry of the residue buffers for an N x N Gram: tile height / width, tile rows, and the number of
+ * tiles that touch the upper triangle.  A residue buffer holds moduli * numTiles * tileY * tileX bytes. */
+void hyacinB200TileInfo(int32_t N, int32_t* tileY, int32_t* tileX, int32_t* tilesY, int32_t* numTiles);
+
+/* Quantise `rows` rows of A (column-major, lda in elements) into int8 residue planes
+ * W[modulus][column][part * ldk + row]; ldk is a multiple of 128 and rows [rows, ldk) are zero-filled.
+ * Real input: one part.  Complex input: three parts (re, im, -re).
+ * Stage counterpart in the reference: src/quantize_crt_real.cu:63-99, src/quantize_crt_complex.cu:72-110. */
+void hyacinB200QuantizeCrt(const hyacinHandle_t* handle, hyacinPrecision_t Atype, int32_t rows, int32_t N,
+                           const void* A, int32_t lda, const int32_t* vexp, int32_t moduli, int32_t valueBytes,
+                           int8_t* W, int64_t ldk);
+
+/* Residue Gram: residues[m][tile][y][x] (+)= sum_k W[m][y][ka0 + k] * W[m][x][kb0 + k] mod modulus m.
+ * kRows, ka0, kb0 multiples of 128; kRows <= 130816.
+ * Stage counterpart in the reference: src/hyacin_herk.cpp:163-189 with src/crt_diag_real.cu:13-29. */
+void hyacinB200GramResidues(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const int8_t* W, int64_t ldw,
+                            int64_t planeStride, int32_t ka0, int32_t kb0, int32_t kRows, int32_t accumulate,
+                            uint8_t* residues);
+
+/* Residues -> packed 63-bit-limb integers, Cpanel[orderC][N(N+1)/2] (+)= value.
+ * Stage counterpart in the reference: src/crt_reconstruct_real.cu:94-99. */
+void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const uint8_t* residues,
+                           int32_t beta, int32_t orderC, uint64_t* Cpanel);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HYACIN_B200_H_ */

@@ -1,0 +1,246 @@
+"""GPU parity tests of the quantized-Gram path, through the C ABI.
+
+Every check is bit-exact: column exponents (int32), residue planes (modulo m), residue Grams (bytes), the
+packed integer Gram (uint64 limbs) and the dequantised matrix (raw float bits).  The checker is the CPU oracle
+(``oracle/``) at sizes it finishes in seconds, and the reference's own CUDA library (``oracle/_ref``, when it
+was built) at larger sizes.
+"""
+import numpy as np
+import pytest
+
+from hyacinth_b200 import api
+from oracle import oracle as O
+from tests.helpers import half_roundtrip, random_matrix, to_device_colmajor
+
+pytestmark = pytest.mark.gpu
+
+CRT_MODULI = [256, 255, 253, 251, 247, 241, 239, 233, 229, 227, 223, 217, 211, 199, 197, 193, 191, 181, 179, 173,
+              167, 163, 157, 151]
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _eps_for(atype):
+    return {api.F64: 1e-10, api.F32: 1e-5, api.F16: 1e-2}[atype & ~1]
+
+
+def _oracle_input(A, atype):
+    return half_roundtrip(A, atype) if (atype & ~1) == api.F16 else A
+
+
+def _run_exponents(h, dA, m, n, lda, atype, u, seg_k=None):
+    torch = _torch()
+    if seg_k is not None:
+        h.h.GramSegmentK = seg_k
+    b, s, l = h.segments(m)
+    vexp = torch.full(((b + 1), n), 12345, dtype=torch.int32, device="cuda")
+    h.quantize_scale_batch(b, s, l, n, atype, dA, lda, u, vexp)
+    torch.cuda.synchronize()
+    return (b, s, l), vexp
+
+
+def _run_herk(h, dA, m, n, lda, atype, u, order, cpanels, segs, vexp, beta=0, C=None):
+    torch = _torch()
+    tri = n * (n + 1) // 2
+    if C is None:
+        C = torch.full((cpanels * order, tri), 0x5555555555555555, dtype=torch.int64, device="cuda")
+    h.herk_batch(segs[0], segs[1], segs[2], n, atype, dA, lda, u, vexp, beta, order, C)
+    torch.cuda.synchronize()
+    assert h.status() == 0, "a bounded wait inside the Gram kernel expired"
+    return C
+
+
+CASES = [
+    # (atype, M, N, lda_pad, seg_k, zero_cols)
+    (api.F64, 512, 128, 0, 8192, ()),
+    (api.F64, 1000, 300, 7, 256, (3, 299)),
+    (api.F64, 100, 1, 0, 8192, ()),
+    (api.F64, 257, 129, 1, 100, ()),
+    (api.F32, 700, 260, 3, 8192, (0,)),
+    (api.F16, 384, 96, 2, 128, ()),
+    (api.F64_COMPLEX, 300, 140, 1, 8192, (5,)),
+    (api.F32_COMPLEX, 260, 70, 0, 64, ()),
+    (api.F16_COMPLEX, 200, 33, 1, 8192, ()),
+]
+
+
+@pytest.mark.parametrize("atype,m,n,pad,seg_k,zero_cols", CASES)
+def test_exponents_and_integer_gram_match_oracle(hy, atype, m, n, pad, seg_k, zero_cols):
+    """vexp table and packed integer Gram equal the CPU oracle bit for bit (ragged sizes, zero columns, lda > M)."""
+    rng = np.random.default_rng(1000 + m + n + atype)
+    A = random_matrix(rng, m, n, atype, zero_cols=zero_cols)
+    lda = m + pad
+    dA = to_device_colmajor(A, lda, atype)
+    u, cp, lp, tri = hy.herk_batch_init(_eps_for(atype), m, n, atype)
+    assert (u, cp, lp, tri) == O.herk_init(_eps_for(atype), m, n, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, lda, atype, u, seg_k)
+    Ao = _oracle_input(A, atype)
+    want_vexp = O.column_exponents(Ao, atype, u, *segs)
+    np.testing.assert_array_equal(vexp.cpu().numpy(), want_vexp)
+    C = _run_herk(hy, dA, m, n, lda, atype, u, lp, cp, segs, vexp)
+    want_C = O.gram_exact(Ao, atype, want_vexp[0], lp)
+    np.testing.assert_array_equal(C.cpu().numpy().view(np.uint64), want_C)
+    hy.h.GramSegmentK = 8192
+
+
+def test_beta_accumulates_and_row_blocks_add_up(hy):
+    """C(beta=1) over two row blocks equals C over the stacked matrix (the hook used to stream a tall matrix)."""
+    torch = _torch()
+    rng = np.random.default_rng(7)
+    m, n, atype = 900, 200, api.F64
+    A = random_matrix(rng, m, n, atype)
+    u, cp, lp, tri = hy.herk_batch_init(1e-10, m, n, atype)
+    dA = to_device_colmajor(A)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    C_all = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
+    m1 = 388
+    d1, d2 = to_device_colmajor(A[:m1]), to_device_colmajor(A[m1:])
+    C = _run_herk(hy, d1, m1, n, m1, atype, u, lp, cp, (1, m1, m1), vexp)
+    C = _run_herk(hy, d2, m - m1, n, m - m1, atype, u, lp, cp, (1, m - m1, m - m1), vexp, beta=1, C=C)
+    assert torch.equal(C, C_all)
+
+
+def test_empty_and_negative_budget_define_zero_gram(hy):
+    """No rows, or u < 0: beta = 0 zeroes C and beta = 1 leaves it alone (src/hyacin_herk.cpp:287)."""
+    torch = _torch()
+    n, order = 40, 2
+    tri = n * (n + 1) // 2
+    vexp = torch.zeros((2, n), dtype=torch.int32, device="cuda")
+    dA = torch.ones((n, 64), dtype=torch.float64, device="cuda")
+    C = torch.full((order, tri), 77, dtype=torch.int64, device="cuda")
+    hy.herk_batch(1, 0, 0, n, api.F64, dA, 64, 40, vexp, 1, order, C)
+    torch.cuda.synchronize()
+    assert int((C != 77).sum()) == 0
+    hy.herk_batch(1, 64, 64, n, api.F64, dA, 64, -1, vexp, 0, order, C)
+    torch.cuda.synchronize()
+    assert int(C.abs().sum()) == 0
+    # quantize-scale with u < 0 marks every column as zero and touches only the global row
+    v2 = torch.full((2, n), 5, dtype=torch.int32, device="cuda")
+    hy.quantize_scale_batch(1, 64, 64, n, api.F64, dA, 64, -1, v2)
+    torch.cuda.synchronize()
+    assert int((v2[0] != 2**31 - 1).sum()) == 0 and int((v2[1] != 5).sum()) == 0
+
+
+@pytest.mark.parametrize("atype,u", [(api.F64, 40), (api.F64, 59), (api.F64, 70), (api.F32, 23), (api.F64_COMPLEX, 47), (api.F16, 12)])
+def test_quantize_stage_residues(hy, atype, u):
+    """Residue planes are congruent to rint(a 2^vexp) modulo every modulus, and the padding rows are zero."""
+    torch = _torch()
+    rng = np.random.default_rng(50 + u)
+    m, n = 203, 17
+    A = random_matrix(rng, m, n, atype, zero_cols=(2,))
+    dA = to_device_colmajor(A, None, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    plan = hy.crt_plan(u, atype & 1, m)
+    k, nb = plan["moduli"], plan["value_bytes"]
+    parts = 3 if atype & 1 else 1
+    ldk = 256
+    W = torch.full((k, n, parts * ldk), 99, dtype=torch.int8, device="cuda")
+    hy.quantize_crt(atype, m, n, dA, m, vexp, k, nb, W, ldk)
+    torch.cuda.synchronize()
+    Wh = W.cpu().numpy().astype(np.int64)
+    q = O.quantize_ints(_oracle_input(A, atype), atype, vexp[0].cpu().numpy())
+    for p in range(parts):
+        src = q[0] if p == 0 else q[1] if p == 1 else [[-v for v in col] for col in q[0]]
+        for i in range(k):
+            want = np.array([[v % CRT_MODULI[i] for v in col] for col in src], dtype=np.int64)
+            got = Wh[i, :, p * ldk:p * ldk + m]
+            assert np.all((got - want) % CRT_MODULI[i] == 0)
+            assert got.min() >= -128 and got.max() <= 127
+            assert np.all(Wh[i, :, p * ldk + m:(p + 1) * ldk] == 0)
+
+
+@pytest.mark.parametrize("n,k_rows,moduli", [(128, 128, 1), (300, 512, 3), (700, 1024, 13), (1030, 256, 24)])
+def test_gram_residue_kernel_against_integer_matmul(hy, n, k_rows, moduli):
+    """tcgen05 residue Gram == plain integer matmul modulo m, for every tile, with and without accumulation."""
+    torch = _torch()
+    rng = np.random.default_rng(n + k_rows)
+    W = torch.from_numpy(rng.integers(-128, 128, size=(moduli, n, k_rows), dtype=np.int8)).cuda()
+    info = hy.tile_info(n)
+    ty, tx, nt = info["tile_y"], info["tile_x"], info["num_tiles"]
+    R = torch.full((moduli, nt, ty, tx), 0xEE, dtype=torch.uint8, device="cuda")
+    hy.gram_residues(n, moduli, W, k_rows, k_rows * n, 0, 0, k_rows, 0, R)
+    hy.gram_residues(n, moduli, W, k_rows, k_rows * n, 0, 0, k_rows, 1, R)     # accumulate the same chunk again
+    torch.cuda.synchronize()
+    assert hy.status() == 0
+    Rh = R.cpu().numpy().astype(np.int64)
+    Wd = W.to(torch.float64)
+    tiles_y = info["tiles_y"]
+    t = 0
+    for bx in range((n + tx - 1) // tx):
+        for by in range(min(tiles_y, 2 * bx + 2)):
+            ys, xs = slice(by * ty, min(n, (by + 1) * ty)), slice(bx * tx, min(n, (bx + 1) * tx))
+            for i in range(moduli):
+                G = (Wd[i, ys] @ Wd[i, xs].T).cpu().numpy().astype(np.int64)     # exact: |sum| < 2^53
+                want = (2 * G) % CRT_MODULI[i]
+                got = Rh[i, t, :G.shape[0], :G.shape[1]]
+                np.testing.assert_array_equal(got, want)
+            t += 1
+    assert t == nt
+
+
+@pytest.mark.parametrize("atype", [api.F64, api.F64_COMPLEX, api.F32])
+def test_dequantize_matches_oracle_bits(hy, atype):
+    """Gram format choice and every bit of the dequantised matrix equal the oracle's (same operation order)."""
+    torch = _torch()
+    rng = np.random.default_rng(99 + atype)
+    m, n = 640, 150
+    A = random_matrix(rng, m, n, atype, zero_cols=(7,))
+    dA = to_device_colmajor(A)
+    eps = _eps_for(atype)
+    u, cp, lp, tri = hy.herk_batch_init(eps, m, n, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    C = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
+    gtype, gbytes = hy.dequantize_init(n, lp, C, vexp, atype)
+    Ch, vh = C.cpu().numpy().view(np.uint64), vexp[0].cpu().numpy()
+    want_g, want_b, _ = O.dequantize_init(Ch, vh, n, lp, atype, corr=7, f64_capable=1)
+    assert (gtype, gbytes) == (want_g, want_b)
+    ldg = n + 3
+    G = torch.zeros((n, ldg * gbytes), dtype=torch.uint8, device="cuda")
+    hy.dequantize(n, lp, C, vexp, gtype, G, ldg)
+    torch.cuda.synchronize()
+    want = O.dequantize(Ch, vh, n, lp, gtype)
+    got = G.cpu().numpy()[:, :n * gbytes].reshape(n, n, gbytes)
+    np.testing.assert_array_equal(got, want.view(np.uint8).reshape(n, n, gbytes))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Side by side with the reference's CUDA library
+# ---------------------------------------------------------------------------------------------------------
+
+REF_CASES = [
+    (api.F64, 20000, 700, 1e-10),
+    (api.F64, 9000, 513, 1e-13),
+    (api.F32, 30000, 520, 1e-5),
+    (api.F64_COMPLEX, 6000, 300, 1e-10),
+    (api.F16, 5000, 256, 1e-2),
+]
+
+
+@pytest.mark.parametrize("atype,m,n,eps", REF_CASES)
+def test_stage_outputs_equal_reference_library(hy, ref, atype, m, n, eps):
+    """Same device buffers through both libraries: vexp, packed integer Gram, Gram format and Gram bits agree."""
+    torch = _torch()
+    rng = np.random.default_rng(4242 + m)
+    A = random_matrix(rng, m, n, atype, zero_cols=(1,), spread_rows=(10.0 if atype == api.F64 else 0.0))
+    dA = to_device_colmajor(A, None, atype)
+    out = []
+    for lib in (hy, ref):
+        u, cp, lp, tri = lib.herk_batch_init(eps, m, n, atype)
+        segs, vexp = _run_exponents(lib, dA, m, n, m, atype, u)
+        C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
+        lib.herk_batch(segs[0], segs[1], segs[2], n, atype, dA, m, u, vexp, 0, lp, C)
+        torch.cuda.synchronize()
+        gtype, gbytes = lib.dequantize_init(n, lp, C, vexp, atype)
+        G = torch.zeros((n, n * gbytes), dtype=torch.uint8, device="cuda")
+        lib.dequantize(n, lp, C, vexp, gtype, G, n)
+        torch.cuda.synchronize()
+        out.append(((u, cp, lp, tri), vexp, C, (gtype, gbytes), G))
+    assert hy.status() == 0
+    assert out[0][0] == out[1][0]
+    assert torch.equal(out[0][1], out[1][1]), "column exponents differ from the reference"
+    assert torch.equal(out[0][2], out[1][2]), "packed integer Gram differs from the reference"
+    assert out[0][3] == out[1][3]
+    assert torch.equal(out[0][4], out[1][4]), "dequantised Gram bits differ from the reference"
