@@ -1,0 +1,282 @@
+// Truncated pivoted Cholesky of the Gram matrix: G(perm, perm) ~= R^H R, R upper trapezoidal with `rank` rows.
+//
+// Downstream of the quantized Gram and replicated on every rank; kept behaviourally equal to the reference's
+// src/hyacin_potrfp.cu: diagonal pivoting on the largest remaining diagonal entry (:214-272), stop as soon
+// as the remaining trace drops to eps^2 times the initial trace (:262) or the rank cap is reached, arithmetic
+// in the Gram's own format (float, double or double-double; helpers as in include/internal.hpp:181-227).
+//
+// The organisation is different.  The reference swaps rows and columns of G in place and computes each new
+// row with one block-wide reduction per column and two or three grid barriers per step.  Here the factor is
+// written to a separate row-major array R[k][i] indexed by ORIGINAL column i (no swaps; the permutation is
+// only recorded), a warp owns 32 consecutive columns so that every load of a previous row is one contiguous
+// run, the sum over previous rows is split across the warps of a block and combined in a fixed order, and a
+// step costs ONE grid barrier: every block re-reduces the per-block (max, argmax, trace) partials itself.
+#include "hyb_internal.h"
+#include "tail.h"
+#include <cooperative_groups.h>
+#include <cfloat>
+
+namespace cg = cooperative_groups;
+
+namespace hyb {
+namespace {
+
+// ---- scalar policies ------------------------------------------------------------------------------------
+struct DD { double x, y; };
+
+__device__ __forceinline__ DD dd_renorm(double a, double b) { double s = a + b, d = a - s; return DD{s, b + d}; }
+__device__ __forceinline__ DD dd_mul(DD a, DD b) { double p = a.x * b.x; return dd_renorm(p, fma(a.x, b.y, a.y * b.x) + fma(a.x, b.x, -p)); }
+__device__ __forceinline__ DD dd_sqr(DD a) { double p = a.x * a.x; return dd_renorm(p, fma(a.x + a.x, a.y, fma(a.x, a.x, -p))); }
+__device__ __forceinline__ DD dd_add(DD a, DD b) {
+  double s = a.x + b.x, d = a.x - s, sd = s + d, e = (b.x + d) + (a.x - sd); return dd_renorm(s, (a.y + b.y) + e);
+}
+__device__ __forceinline__ DD dd_sub(DD a, DD b) {
+  double nb = -b.x, s = a.x + nb, d = a.x - s, sd = s + d, e = (nb + d) + (a.x - sd); return dd_renorm(s, (a.y - b.y) + e);
+}
+
+template <typename R> struct Real;
+template <> struct Real<float> {
+  static __device__ __forceinline__ float zero() { return 0.f; }
+  static __device__ __forceinline__ float mul(float a, float b) { return a * b; }
+  static __device__ __forceinline__ float add(float a, float b) { return a + b; }
+  static __device__ __forceinline__ float sub(float a, float b) { return a - b; }
+  static __device__ __forceinline__ float neg(float a) { return -a; }
+  static __device__ __forceinline__ float fnma(float a, float b, float c) { return fmaf(-a, b, c); }      // c - a b
+  static __device__ __forceinline__ bool less(float a, float b) { return a < b; }
+  static __device__ __forceinline__ double to_double(float a) { return double(a); }
+  static __device__ __forceinline__ float rsqrt(float a) { return 1.f / sqrtf(a); }
+};
+template <> struct Real<double> {
+  static __device__ __forceinline__ double zero() { return 0.; }
+  static __device__ __forceinline__ double mul(double a, double b) { return a * b; }
+  static __device__ __forceinline__ double add(double a, double b) { return a + b; }
+  static __device__ __forceinline__ double sub(double a, double b) { return a - b; }
+  static __device__ __forceinline__ double neg(double a) { return -a; }
+  static __device__ __forceinline__ double fnma(double a, double b, double c) { return fma(-a, b, c); }
+  static __device__ __forceinline__ bool less(double a, double b) { return a < b; }
+  static __device__ __forceinline__ double to_double(double a) { return a; }
+  static __device__ __forceinline__ double rsqrt(double a) { return 1. / sqrt(a); }
+};
+template <> struct Real<DD> {
+  static __device__ __forceinline__ DD zero() { return DD{0., 0.}; }
+  static __device__ __forceinline__ DD mul(DD a, DD b) { return dd_mul(a, b); }
+  static __device__ __forceinline__ DD add(DD a, DD b) { return dd_add(a, b); }
+  static __device__ __forceinline__ DD sub(DD a, DD b) { return dd_sub(a, b); }
+  static __device__ __forceinline__ DD neg(DD a) { return DD{-a.x, -a.y}; }
+  static __device__ __forceinline__ DD fnma(DD a, DD b, DD c) { return dd_sub(c, dd_mul(a, b)); }
+  static __device__ __forceinline__ bool less(DD a, DD b) { return a.x < b.x || (a.x == b.x && a.y < b.y); }
+  static __device__ __forceinline__ double to_double(DD a) { return a.x; }
+  // 1/sqrt(a) to double-double accuracy: two Newton steps y <- y (3/2 - a y^2 / 2) from the double estimate.
+  static __device__ __forceinline__ DD rsqrt(DD a) {
+    DD y{1. / sqrt(a.x), 0.}; const DD half_a{0.5 * a.x, 0.5 * a.y};
+#pragma unroll
+    for (int it = 0; it < 2; ++it) y = dd_mul(y, dd_sub(DD{1.5, 0.}, dd_mul(half_a, dd_sqr(y))));
+    return y;
+  }
+};
+
+template <typename R, bool CPLX> struct Elem { R re; };
+template <typename R> struct Elem<R, true> { R re, im; };
+
+template <typename R, bool CPLX> struct Ops {
+  using E = Elem<R, CPLX>; using T = Real<R>;
+  static __device__ __forceinline__ E zero() { E z; z.re = T::zero(); if constexpr (CPLX) z.im = T::zero(); return z; }
+  static __device__ __forceinline__ E conj(E a) { if constexpr (CPLX) a.im = T::neg(a.im); return a; }
+  // acc - conj(a) * b
+  static __device__ __forceinline__ E sub_conj_mul(E acc, E a, E b) {
+    if constexpr (CPLX) {
+      // conj(a) b = (ar br + ai bi) + i (ar bi - ai br)
+      acc.re = T::fnma(a.re, b.re, acc.re); acc.re = T::fnma(a.im, b.im, acc.re);
+      acc.im = T::fnma(a.re, b.im, acc.im); acc.im = T::add(acc.im, T::mul(a.im, b.re));
+    } else acc.re = T::fnma(a.re, b.re, acc.re);
+    return acc;
+  }
+  static __device__ __forceinline__ E add(E a, E b) { a.re = T::add(a.re, b.re); if constexpr (CPLX) a.im = T::add(a.im, b.im); return a; }
+  static __device__ __forceinline__ E scale(E a, R s) { a.re = T::mul(a.re, s); if constexpr (CPLX) a.im = T::mul(a.im, s); return a; }
+  static __device__ __forceinline__ R abs2(E a) { R v = T::mul(a.re, a.re); if constexpr (CPLX) v = T::add(v, T::mul(a.im, a.im)); return v; }
+};
+
+constexpr int kBlock = 512;               // 16 warps: 32 columns per block, previous rows split 16 ways
+constexpr int kWarps = kBlock / 32;
+constexpr int kChunk = 256;               // previous rows staged per shared-memory pass
+
+template <typename R, bool CPLX>
+struct Partial { R val; double trace; int idx; int pad; };
+
+// jpiv (1-based) is kept as a permutation that is updated by swapping the chosen column into position k, which
+// is the bookkeeping of the reference (src/hyacin_potrfp.cu:243-246), so the whole array -- not only its first
+// `rank` entries -- comes out the same.  pos[i] is the inverse map: column i is still free while pos[i] >= k.
+template <typename R, bool CPLX>
+__global__ void __launch_bounds__(kBlock)
+potrfp_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restrict__ G, int64_t ldg, Elem<R, CPLX>* __restrict__ Rw,
+              R* __restrict__ D, int* __restrict__ pos, int32_t* __restrict__ jpiv, Partial<R, CPLX>* __restrict__ partials,
+              int32_t* __restrict__ rank_out) {
+  using E = Elem<R, CPLX>; using O = Ops<R, CPLX>; using T = Real<R>; using P = Partial<R, CPLX>;
+  cg::grid_group grid = cg::this_grid();
+  __shared__ E s_pivot_row[kChunk];                 // conj-multiplier: previous rows at the pivot column
+  __shared__ E s_partial[kWarps][32];
+  __shared__ P s_red[kWarps];
+  __shared__ P s_best;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblocks = gridDim.x;
+
+  // ---- step "-1": diagonal, initial partials ----
+  {
+    P mine; mine.val = T::zero(); mine.trace = 0.; mine.idx = -1; mine.pad = 0;
+    for (int i = blockIdx.x * kBlock + threadIdx.x; i < n; i += nblocks * kBlock) {
+      const R d = G[i + int64_t(i) * ldg].re;
+      D[i] = d; pos[i] = i; jpiv[i] = i + 1;
+      mine.trace += T::to_double(d);
+      if (mine.idx < 0 || T::less(mine.val, d)) { mine.val = d; mine.idx = i; }
+    }
+    // block reduce (fixed order: lane tree then warp 0 over warps)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      P other; other.trace = __shfl_down_sync(0xffffffffu, mine.trace, o); other.idx = __shfl_down_sync(0xffffffffu, mine.idx, o);
+      if constexpr (sizeof(R) == 16) { other.val.x = __shfl_down_sync(0xffffffffu, mine.val.x, o); other.val.y = __shfl_down_sync(0xffffffffu, mine.val.y, o); }
+      else other.val = __shfl_down_sync(0xffffffffu, mine.val, o);
+      mine.trace += other.trace;
+      if (other.idx >= 0 && (mine.idx < 0 || T::less(mine.val, other.val))) { mine.val = other.val; mine.idx = other.idx; }
+    }
+    if (lane == 0) s_red[warp] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      P acc = s_red[0];
+      for (int w = 1; w < kWarps; ++w) { acc.trace += s_red[w].trace; if (s_red[w].idx >= 0 && (acc.idx < 0 || T::less(acc.val, s_red[w].val))) { acc.val = s_red[w].val; acc.idx = s_red[w].idx; } }
+      partials[blockIdx.x] = acc;
+    }
+  }
+  grid.sync();
+
+  double threshold = 0.;
+  int k = 0;
+  for (;; ++k) {
+    // ---- every block reduces the partials of all blocks in the same order: same pivot everywhere ----
+    const P* cur = partials + size_t(k & 1) * nblocks;
+    if (threadIdx.x == 0) {
+      // volatile reads: these words are rewritten by other blocks every second step
+      const volatile P* vc = cur;
+      P acc; acc.trace = 0.; acc.idx = -1; acc.val = T::zero(); acc.pad = 0;
+      for (int b = 0; b < nblocks; ++b) {
+        P o; o.trace = vc[b].trace; o.idx = vc[b].idx;
+        if constexpr (sizeof(R) == 16) { o.val.x = vc[b].val.x; o.val.y = vc[b].val.y; } else o.val = vc[b].val;
+        acc.trace += o.trace;
+        if (o.idx >= 0 && (acc.idx < 0 || T::less(acc.val, o.val))) { acc.val = o.val; acc.idx = o.idx; }
+      }
+      s_best = acc;
+    }
+    __syncthreads();
+    const P best = s_best;
+    if (k == 0) threshold = eps_sq * best.trace;
+    // stop: nothing left, rank cap reached, remaining trace at or below the threshold, or a non-positive pivot
+    bool stop = best.idx < 0 || k >= cap || (k > 0 && !(threshold < best.trace)) || !(T::to_double(best.val) > 0.);
+    if (stop) break;
+    const int p = best.idx;
+    const R rinv = T::rsqrt(best.val);              // 1 / R[k][p]
+    const R rkk = T::mul(best.val, rinv);           // sqrt(d) = d / sqrt(d)
+    P mine; mine.val = T::zero(); mine.trace = 0.; mine.idx = -1; mine.pad = 0;
+
+    for (int c0 = blockIdx.x * 32; c0 < n; c0 += nblocks * 32) {
+      const int i = c0 + lane;
+      const bool live = i < n && i != p && __ldcg(&pos[i]) >= k;
+      E acc = O::zero();
+      for (int l0 = 0; l0 < k; l0 += kChunk) {
+        const int lc = min(kChunk, k - l0);
+        __syncthreads();
+        for (int t = threadIdx.x; t < lc; t += kBlock) s_pivot_row[t] = Rw[size_t(l0 + t) * n + p];
+        __syncthreads();
+        if (live) for (int t = warp; t < lc; t += kWarps) acc = O::sub_conj_mul(acc, s_pivot_row[t], Rw[size_t(l0 + t) * n + i]);
+      }
+      s_partial[warp][lane] = acc;
+      __syncthreads();
+      if (warp == 0) {
+        E out = O::zero();
+        if (live) {
+          // G[p, i] = conj(G[i, p]): column p of the Hermitian matrix is contiguous
+          E v = O::conj(G[i + int64_t(p) * ldg]);
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) v = O::add(v, s_partial[w][lane]);
+          out = O::scale(v, rinv);
+          const R d = T::sub(D[i], O::abs2(out));
+          D[i] = d;
+          mine.trace += T::to_double(d);
+          if (mine.idx < 0 || T::less(mine.val, d)) { mine.val = d; mine.idx = i; }
+        } else if (i == p) { out.re = rkk; }
+        if (i < n) Rw[size_t(k) * n + i] = out;
+      }
+      __syncthreads();
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      // swap the pivot into position k; both values a displaced column can be seen with are >= k, so readers
+      // of pos[] in other blocks classify it as free either way
+      const int q = pos[p], other = jpiv[k] - 1;
+      jpiv[k] = p + 1; jpiv[q] = other + 1; pos[other] = q; pos[p] = k;
+    }
+    // block-level partial for the next step (only warp 0 holds data)
+    if (warp == 0) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        P other; other.trace = __shfl_down_sync(0xffffffffu, mine.trace, o); other.idx = __shfl_down_sync(0xffffffffu, mine.idx, o);
+        if constexpr (sizeof(R) == 16) { other.val.x = __shfl_down_sync(0xffffffffu, mine.val.x, o); other.val.y = __shfl_down_sync(0xffffffffu, mine.val.y, o); }
+        else other.val = __shfl_down_sync(0xffffffffu, mine.val, o);
+        mine.trace += other.trace;
+        if (other.idx >= 0 && (mine.idx < 0 || T::less(mine.val, other.val))) { mine.val = other.val; mine.idx = other.idx; }
+      }
+      if (lane == 0) partials[size_t((k + 1) & 1) * nblocks + blockIdx.x] = mine;
+    }
+    grid.sync();
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) *rank_out = k;
+}
+
+template <typename R, bool CPLX>
+int run_potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, const void* G, int64_t ldg, void* Rw, int32_t* jpiv) {
+  using E = Elem<R, CPLX>; using P = Partial<R, CPLX>;
+  cudaStream_t stream = handle->cudaStream;
+  int per_sm = 0;
+  HYB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, potrfp_kernel<R, CPLX>, kBlock, 0));
+  int grid = std::max(1, std::min(handle->DeviceSMs * std::max(per_sm, 1), (n + 31) / 32));
+  R* D = nullptr; int* pos = nullptr; P* partials = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&D), size_t(n) * sizeof(R), handle->mempool, stream));
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&pos), size_t(n) * sizeof(int), handle->mempool, stream));
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&partials), size_t(2) * grid * sizeof(P), handle->mempool, stream));
+  int32_t* rank_host = static_cast<int32_t*>(handle->pinnedWorkspace);
+  *rank_host = 0;
+  double eps_sq = eps * eps;
+  const E* g = static_cast<const E*>(G); E* rw = static_cast<E*>(Rw);
+  void* args[] = {&eps_sq, &n, &cap, &g, &ldg, &rw, &D, &pos, &jpiv, &partials, &rank_host};
+  HYB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(potrfp_kernel<R, CPLX>), dim3(grid), dim3(kBlock), args, 0, stream));
+  HYB_CUDA(cudaFreeAsync(D, stream)); HYB_CUDA(cudaFreeAsync(pos, stream)); HYB_CUDA(cudaFreeAsync(partials, stream));
+  HYB_CUDA(cudaStreamSynchronize(stream));
+  return *rank_host;
+}
+
+}  // namespace
+
+size_t gram_elem_bytes(hyacinPrecision_t gtype) {
+  static const int bytes[12] = {8, 16, 4, 8, 2, 4, 16, 32, 12, 24, 16, 32};
+  return (int(gtype) >= 0 && int(gtype) < 12) ? size_t(bytes[int(gtype)]) : 0;
+}
+
+int potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, hyacinPrecision_t gtype, const void* G, int64_t ldg,
+           void* Rw, int32_t* jpiv) {
+  int rank = -1;
+  switch (gtype) {
+    case HYACIN_F32: rank = run_potrfp<float, false>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    case HYACIN_F64: rank = run_potrfp<double, false>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    case HYACIN_DD: rank = run_potrfp<DD, false>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    case HYACIN_F32_COMPLEX: rank = run_potrfp<float, true>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    case HYACIN_F64_COMPLEX: rank = run_potrfp<double, true>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    case HYACIN_DD_COMPLEX: rank = run_potrfp<DD, true>(handle, eps, cap, n, G, ldg, Rw, jpiv); break;
+    default:
+      std::fprintf(stderr, "hyacin-b200: Gram format %d (triple-/quad-float) is only produced on GPUs without fast FP64 and is not supported here\n", int(gtype));
+      return 0;
+  }
+  if (handle->logger) {
+    static const char* names[12] = {"FP64", "FP64-COMPLEX", "FP32", "FP32-COMPLEX", "", "", "FP128-DD", "FP128-DD-COMPLEX", "", "", "", ""};
+    std::fprintf(static_cast<FILE*>(handle->logger), "POTRFP-%s [eps=%.1le] [N=%d] [K=%d] [Cholesky-rank=%d]\n", names[int(gtype)], eps, n, cap, rank);
+  }
+  return rank;
+}
+
+}  // namespace hyb

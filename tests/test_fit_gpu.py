@@ -1,0 +1,213 @@
+"""GPU tests of the fits behind the public entry points: hyacinTsvdFit, hyacinTsvdFitSegmentN,
+hyacinInterpolateFit, hyacinCheckNorm, and the replicated stage functions hyacinXGevd / hyacinXGinterp.
+
+Checked against host LAPACK (numpy) on the small BASELINE configuration and, side by side, against the
+reference's own CUDA library: identical rank and pivots, singular values within 1e-12 relative for FP64
+(1e-5 for FP32), relative projection error <= eps.
+"""
+import numpy as np
+import pytest
+
+from hyacinth_b200 import api
+from tests.helpers import low_rank_matrix, random_matrix, to_device_colmajor
+
+pytestmark = pytest.mark.gpu
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _real_dtype(atype):
+    torch = _torch()
+    return {api.F64: torch.float64, api.F32: torch.float32, api.F16: torch.float16}[atype & ~1]
+
+
+def _alloc_v(n, k, atype):
+    torch = _torch()
+    words = 2 if atype & 1 else 1
+    return torch.zeros((k, n * words), dtype=_real_dtype(atype), device="cuda")
+
+
+def _tsvd(lib, dA, op, m, n, k, lda, eps, atype, global_m=None, segment_n=False):
+    torch = _torch()
+    S = torch.zeros(k, dtype=_real_dtype(atype), device="cuda")
+    V = _alloc_v(n, k, atype)
+    rank = lib.tsvd_fit(eps, op, m, n, k, dA, lda, S, V, n, global_m or m, atype, segment_n=segment_n)
+    torch.cuda.synchronize()
+    return rank, S, V
+
+
+def _rel_error(lib, dA, op, m, n, lda, rank, V, atype):
+    tot = lib.check_norm(op, m, n, dA, lda, 0, None, 0, atype)
+    res = lib.check_norm(op, m, n, dA, lda, rank, V, n, atype)
+    return float(np.sqrt(res / tot)) if tot > 0 else 0.0
+
+
+def test_tsvd_fit_small_configuration_against_lapack(hy):
+    """512 x 128 FP64, rank-16 spectrum 10^(-12 i / 15), noise 1e-14, eps 1e-10: rank 16, sigma to 1e-12 relative."""
+    rng = np.random.default_rng(20240611 + 1)
+    m, n, k, eps = 512, 128, 128, 1e-10
+    sigma = 10.0 ** (-12.0 * np.arange(16) / 15.0)
+    A = low_rank_matrix(rng, m, n, 16, sigma, 1e-14)
+    dA = to_device_colmajor(A)
+    rank, S, V = _tsvd(hy, dA, "N", m, n, k, m, eps, api.F64)
+    s_ref = np.linalg.svd(A, compute_uv=False)
+    tail = np.sqrt(np.cumsum((s_ref ** 2)[::-1])[::-1])
+    want_rank = int((tail > eps * tail[0]).sum())
+    assert rank == want_rank
+    got = S.cpu().numpy()
+    assert np.all(got[rank:] == 0)
+    # singular values relative to the largest one: the Gram route resolves sigma_i / sigma_1 down to about eps
+    assert np.max(np.abs(got[:rank] - s_ref[:rank]) / s_ref[0]) < 1e-12
+    assert np.max(np.abs(got[:8] - s_ref[:8]) / s_ref[:8]) < 1e-9
+    Vh = V.cpu().numpy()[:rank].T          # n x rank
+    assert np.abs(Vh.T @ Vh - np.eye(rank)).max() < 1e-10
+    assert _rel_error(hy, dA, "N", m, n, m, rank, V, api.F64) <= eps
+    assert hy.status() == 0
+
+
+FIT_CASES = [
+    # (atype, op, M, N, K, eps, tolS)
+    (api.F64, "N", 512, 128, 128, 1e-10, 1e-12),
+    (api.F64, "T", 3000, 200, 150, 1e-8, 1e-12),
+    (api.F32, "N", 4000, 256, 256, 1e-4, 1e-5),
+    (api.F64_COMPLEX, "C", 2000, 160, 160, 1e-9, 1e-12),
+    (api.F32_COMPLEX, "N", 1500, 96, 64, 1e-3, 1e-5),
+]
+
+
+def _decaying_matrix(rng, m, n, atype, decades):
+    r = min(m, n)
+    U, _ = np.linalg.qr(rng.standard_normal((m, r)) + (1j * rng.standard_normal((m, r)) if atype & 1 else 0))
+    Vm, _ = np.linalg.qr(rng.standard_normal((n, r)) + (1j * rng.standard_normal((n, r)) if atype & 1 else 0))
+    s = 10.0 ** (-decades * np.arange(r) / (r - 1))
+    A = (U * s) @ Vm.conj().T
+    A = A * 10.0 ** rng.uniform(-2, 2, size=n)
+    from tests.helpers import NP_DTYPE
+    return A.astype(NP_DTYPE[atype])
+
+
+@pytest.mark.parametrize("atype,op,m,n,k,eps,tol", FIT_CASES)
+def test_tsvd_fit_matches_reference_library(hy, ref, atype, op, m, n, k, eps, tol):
+    """Same buffers through both libraries: identical rank, singular values within tolerance, error <= eps."""
+    rng = np.random.default_rng(77 + m)
+    A = _decaying_matrix(rng, m, n, atype, 12.0 if (atype & ~1) == api.F64 else 6.0)
+    stored = A if op == "N" else (A.T if op == "T" else A.conj().T)
+    stored = np.ascontiguousarray(stored)
+    dA = to_device_colmajor(stored)
+    lda = stored.shape[0]
+    r1, S1, V1 = _tsvd(hy, dA, op, m, n, k, lda, eps, atype)
+    r2, S2, V2 = _tsvd(ref, dA, op, m, n, k, lda, eps, atype)
+    assert r1 == r2, (r1, r2)
+    s1, s2 = S1.cpu().numpy().astype(np.float64), S2.cpu().numpy().astype(np.float64)
+    assert np.max(np.abs(s1 - s2)) <= tol * s2[0]
+    e1 = _rel_error(hy, dA, op, m, n, lda, r1, V1, atype)
+    e2 = _rel_error(ref, dA, op, m, n, lda, r2, V2, atype)
+    assert e1 <= max(eps, 1.05 * e2)
+    assert hy.status() == 0
+
+
+def test_check_norm_matches_reference_and_numpy(hy, ref):
+    rng = np.random.default_rng(5)
+    m, n, r = 2500, 120, 30
+    A = random_matrix(rng, m, n, api.F64, col_scale_decades=1.0)
+    V = np.linalg.qr(rng.standard_normal((n, r)))[0] @ rng.standard_normal((r, r))      # not orthonormal on purpose
+    dA, dV = to_device_colmajor(A), to_device_colmajor(V)
+    Q = np.linalg.qr(V)[0]
+    want = np.linalg.norm(A - A @ Q @ Q.T) ** 2
+    got = hy.check_norm("N", m, n, dA, m, r, dV, n, api.F64)
+    got_ref = ref.check_norm("N", m, n, dA, m, r, dV, n, api.F64)
+    assert abs(got - want) <= 1e-10 * want and abs(got - got_ref) <= 1e-12 * want
+    assert abs(hy.check_norm("N", m, n, dA, m, 0, None, 0, api.F64) - np.linalg.norm(A) ** 2) <= 1e-12 * np.linalg.norm(A) ** 2
+    dAt = to_device_colmajor(np.ascontiguousarray(A.T))
+    assert abs(hy.check_norm("T", m, n, dAt, n, r, dV, n, api.F64) - want) <= 1e-10 * want
+
+
+@pytest.mark.parametrize("atype,op,m,n,k,eps", [
+    (api.F32, "T", 6000, 512, 96, 1e-5),
+    (api.F64, "N", 3000, 300, 300, 1e-9),
+    (api.F64_COMPLEX, "N", 1200, 100, 40, 1e-8),
+])
+def test_interpolate_fit_pivots_identical_to_reference(hy, ref, atype, op, m, n, k, eps):
+    """One-based pivots and rank are identical; the interpolation basis reproduces the matrix to eps."""
+    torch = _torch()
+    rng = np.random.default_rng(31 + n)
+    inner = 60 if k < n else n
+    A = rng.standard_normal((m, inner)) @ rng.standard_normal((inner, n)) + 1e-7 * rng.standard_normal((m, n))
+    if atype & 1:
+        A = A + 1j * (rng.standard_normal((m, inner)) @ rng.standard_normal((inner, n)))
+    A = A * 10.0 ** rng.uniform(-2, 2, size=n)
+    from tests.helpers import NP_DTYPE
+    A = A.astype(NP_DTYPE[atype])
+    stored = np.ascontiguousarray(A if op == "N" else A.T)
+    dA = to_device_colmajor(stored)
+    lda = stored.shape[0]
+    out = []
+    for lib in (hy, ref):
+        jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+        V = _alloc_v(n, k, atype)
+        rank = lib.interpolate_fit(eps, op, m, n, k, dA, lda, jp, V, n, m, atype)
+        torch.cuda.synchronize()
+        out.append((rank, jp, V))
+    assert out[0][0] == out[1][0]
+    rank = out[0][0]
+    assert torch.equal(out[0][1], out[1][1]), "pivots differ from the reference"
+    V1, V2 = out[0][2].cpu().numpy()[:rank], out[1][2].cpu().numpy()[:rank]
+    assert np.max(np.abs(V1.astype(np.float64) - V2.astype(np.float64))) <= (1e-4 if (atype & ~1) == api.F32 else 1e-9) * max(1.0, np.abs(V2).max())
+    if rank < k or k == n:
+        err = _rel_error(hy, dA, op, m, n, lda, rank, out[0][2], atype)
+        assert err <= 10 * eps
+    assert hy.status() == 0
+
+
+def test_segmented_fit_matches_reference(hy, ref):
+    """hyacinTsvdFitSegmentN on a complex conjugate-transposed input with two column segments."""
+    rng = np.random.default_rng(404)
+    m, n, k, eps, atype = 4096, 1024, 128, 1e-9, api.F64_COMPLEX
+    r = 100
+    U = np.linalg.qr(rng.standard_normal((m, r)) + 1j * rng.standard_normal((m, r)))[0]
+    W = np.linalg.qr(rng.standard_normal((n, r)) + 1j * rng.standard_normal((n, r)))[0]
+    s = 10.0 ** (-13.0 * np.arange(r) / (r - 1))
+    A = ((U * s) @ W.conj().T + 1e-15 * rng.standard_normal((m, n))).astype(np.complex128)
+    stored = np.ascontiguousarray(A.conj().T)                 # N x M, passed with opA = 'C'
+    dA = to_device_colmajor(stored)
+    r1, S1, V1 = _tsvd(hy, dA, "C", m, n, k, n, eps, atype, segment_n=True)
+    r2, S2, V2 = _tsvd(ref, dA, "C", m, n, k, n, eps, atype, segment_n=True)
+    assert r1 == r2
+    s1, s2 = S1.cpu().numpy(), S2.cpu().numpy()
+    assert np.max(np.abs(s1 - s2)) <= 1e-12 * s2[0]
+    assert _rel_error(hy, dA, "C", m, n, n, r1, V1, atype) <= eps
+    assert hy.status() == 0
+
+
+def test_stage_functions_on_a_shared_gram(hy, ref):
+    """hyacinXGevd and hyacinXGinterp of both libraries on bit-identical Gram matrices."""
+    torch = _torch()
+    rng = np.random.default_rng(9)
+    m, n, k, eps, atype = 5000, 400, 400, 1e-10, api.F64
+    A = _decaying_matrix(rng, m, n, atype, 14.0)
+    dA = to_device_colmajor(A)
+    res = []
+    for lib in (hy, ref):
+        u, cp, lp, tri = lib.herk_batch_init(eps, m, n, atype)
+        b, s, l = lib.segments(m)
+        vexp = torch.zeros((b + 1, n), dtype=torch.int32, device="cuda")
+        C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
+        lib.quantize_scale_batch(b, s, l, n, atype, dA, m, u, vexp)
+        lib.herk_batch(b, s, l, n, atype, dA, m, u, vexp, 0, lp, C)
+        gtype, gbytes = lib.dequantize_init(n, lp, C, vexp, atype)
+        G = torch.zeros((n, n * gbytes), dtype=torch.uint8, device="cuda")
+        lib.dequantize(n, lp, C, vexp, gtype, G, n)
+        G2 = G.clone()
+        S = torch.zeros(k, dtype=torch.float64, device="cuda"); X = torch.zeros((k, n), dtype=torch.float64, device="cuda")
+        r_svd = lib.gevd(eps, n, k, atype, X, n, S, gtype, G, n)
+        jp = torch.zeros(n, dtype=torch.int32, device="cuda"); Xi = torch.zeros((k, n), dtype=torch.float64, device="cuda")
+        r_id = lib.ginterp(eps, n, 64, atype, Xi, n, jp, gtype, G2, n)
+        torch.cuda.synchronize()
+        res.append((r_svd, S, r_id, jp))
+    assert res[0][0] == res[1][0] and res[0][2] == res[1][2] == 64
+    assert torch.equal(res[0][3], res[1][3])
+    s1, s2 = res[0][1].cpu().numpy(), res[1][1].cpu().numpy()
+    assert np.max(np.abs(s1 - s2)) <= 1e-12 * s2[0]
