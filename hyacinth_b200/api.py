@@ -29,7 +29,8 @@ PUBLIC_SYMBOLS = [
 ]
 B200_SYMBOLS = [
     "hyacinB200Status", "hyacinB200CrtPlan", "hyacinB200TileInfo", "hyacinB200QuantizeCrt",
-    "hyacinB200GramResidues", "hyacinB200Reconstruct",
+    "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
+    "hyacinB200ProfileRead", "hyacinB200SlicePlan",
 ]
 
 
@@ -78,6 +79,10 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200QuantizeCrt": (None, [H, i32, i32, i32, vp, i32, vp, i32, i32, vp, i64]),
         "hyacinB200GramResidues": (None, [H, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp]),
         "hyacinB200Reconstruct": (None, [H, i32, i32, vp, i32, i32, vp]),
+        "hyacinB200SlicePlan": (None, [i32, i32, POINTER(i32), POINTER(i32)]),
+        "hyacinB200LaunchCount": (i64, [i32]),
+        "hyacinB200ProfileEnable": (None, [i32]),
+        "hyacinB200ProfileRead": (None, [POINTER(f64), POINTER(i32), POINTER(f64), POINTER(i32)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name, None)
@@ -184,6 +189,17 @@ class Hyacin:
     # ---- B200-only stage entry points ----------------------------------------------------------------
     def status(self, clear: bool = True) -> int:
         return int(self.lib.hyacinB200Status(1 if clear else 0))
+
+    def launch_count(self, reset: bool = False) -> int:
+        return int(self.lib.hyacinB200LaunchCount(1 if reset else 0))
+
+    def profile_enable(self, on: bool):
+        self.lib.hyacinB200ProfileEnable(1 if on else 0)
+
+    def profile_read(self):
+        gm, gn, qm, qn = c_double(), c_int32(), c_double(), c_int32()
+        self.lib.hyacinB200ProfileRead(byref(gm), byref(gn), byref(qm), byref(qn))
+        return {"gram_ms": gm.value, "gram_launches": gn.value, "quantize_ms": qm.value, "quantize_launches": qn.value}
 
     def crt_plan(self, u: int, cplx: int, rows: int):
         a, b, c, d = c_int32(), c_int32(), c_int32(), c_int32()

@@ -10,6 +10,7 @@
 // case.  Integer addition is associative, so the result does not depend on rank order or on the algorithm
 // NCCL picks (ring, tree or in-switch reduction).
 #include "hyb_internal.h"
+#include <hyacin_b200.h>
 
 namespace hyb {
 
@@ -89,19 +90,28 @@ slices_to_limbs_kernel(int order, SlicePlan plan, uint64_t count, const uint64_t
 }  // namespace
 
 int slice_count(int order, int ranks) { return slice_plan(order, ranks).slices; }
+void slice_layout(int order, int ranks, int* slices, int* width) { const SlicePlan p = slice_plan(order, ranks); *slices = p.slices; *width = p.width; }
 
 void launch_limbs_to_slices(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* A, uint64_t* S) {
   dim3 grid(unsigned((count + 255) / 256), unsigned(panels));
+  count_launch();
   limbs_to_slices_kernel<<<grid, 256, 0, stream>>>(order, slice_plan(order, ranks), count, A, S);
   HYB_CUDA(cudaGetLastError());
 }
 void launch_slices_to_limbs(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* S, uint64_t* A) {
   dim3 grid(unsigned((count + 255) / 256), unsigned(panels));
+  count_launch();
   slices_to_limbs_kernel<<<grid, 256, 0, stream>>>(order, slice_plan(order, ranks), count, S, A);
   HYB_CUDA(cudaGetLastError());
 }
 
 }  // namespace hyb
+
+extern "C" void hyacinB200SlicePlan(int32_t orderA, int32_t ranks, int32_t* slices, int32_t* widthBits) {
+  int s = 0, w = 0;
+  if (orderA >= 1 && orderA <= 3 && ranks >= 1) hyb::slice_layout(orderA, ranks, &s, &w);
+  if (slices) *slices = s; if (widthBits) *widthBits = w;
+}
 
 #ifdef HYACIN_BUILD_NO_NCCL
 extern "C" void hyacinAllReduce1Drow(const hyacinHandle_t*, int32_t, int32_t, uint64_t, uint64_t*) {}

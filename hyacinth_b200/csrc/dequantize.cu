@@ -195,6 +195,7 @@ void run_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C, co
 
 void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, int32_t* bits_out) {
   const int64_t tri = (int64_t(n) * n + n) / 2;
+  count_launch();
   switch (order) {
     case 1: gram_range_kernel<512, 1><<<1, 512, 0, stream>>>(n, C, tri, vexp, bits_out); break;
     case 2: gram_range_kernel<512, 2><<<1, 512, 0, stream>>>(n, C, tri, vexp, bits_out); break;
@@ -206,6 +207,7 @@ void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C,
 
 void launch_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp,
                        hyacinPrecision_t gtype, void* G, int64_t ldg) {
+  count_launch();
   switch (gtype) {
     case HYACIN_F64: run_dequantize<double, false>(stream, n, order, C, vexp, G, ldg); break;
     case HYACIN_F32: run_dequantize<float, false>(stream, n, order, C, vexp, G, ldg); break;

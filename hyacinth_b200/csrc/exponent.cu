@@ -152,7 +152,9 @@ void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int b
   // Without rows or with a negative bit budget only the global row is defined (all columns "zero").
   int64_t count = empty ? int64_t(n) : int64_t(batches + 1) * n;
   fill_i32_kernel<<<unsigned((count + 255) / 256), 256, 0, stream>>>(vexp, count, INT_MAX);
+  count_launch();
   if (empty) return;
+  count_launch();
   const int cplx = is_complex(atype);
   switch (base_type(atype)) {
     case HYACIN_F64: run_exponents<double>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;
@@ -166,6 +168,7 @@ void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int b
 void launch_vector_range(cudaStream_t stream, int batches, int n, int u, const int32_t* vexp, int32_t* seg_u) {
   if (batches <= 0) return;
   vector_range_kernel<<<batches, 256, 0, stream>>>(n, u, vexp, seg_u);
+  count_launch();
   HYB_CUDA(cudaGetLastError());
 }
 

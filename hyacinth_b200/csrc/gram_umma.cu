@@ -309,6 +309,8 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
   const int items = g.moduli * tp.num_tiles;
   int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > items) grid = items;
   if (grid <= 0 || p.num_kblocks <= 0) return;
+  ProfileScope prof(stream, KernelKind::Gram);
+  count_launch();
   gram_residue_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
   HYB_CUDA(cudaGetLastError());
 }

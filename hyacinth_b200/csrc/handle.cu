@@ -6,6 +6,9 @@
 // handle; the timer (:39-43, 103-141) records a CUDA event whenever the class of work changes and
 // hyacinSync_TimerSegments reports the milliseconds per class.
 #include "hyb_internal.h"
+#include <hyacin_b200.h>
+#include <atomic>
+#include <mutex>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -29,6 +32,31 @@ struct SegmentTimer {
 const char* env(const char* key) { return std::getenv(key); }
 bool env_true(const char* key) { const char* v = env(key); return v && (!std::strcmp(v, "1") || !std::strcmp(v, "true") || !std::strcmp(v, "True")); }
 }  // namespace
+
+// ---- launch counter and optional per-kernel event profile ---------------------------------------------
+namespace {
+struct ProfileEntry { cudaEvent_t start, stop; KernelKind kind; };
+std::atomic<long long> g_launches{0};
+std::atomic<int> g_profile_on{0};
+std::mutex g_profile_mutex;
+std::vector<ProfileEntry> g_profile;
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+ProfileScope::ProfileScope(cudaStream_t s, KernelKind kind) : stream(s), slot(-1) {
+  if (!g_profile_on.load(std::memory_order_relaxed)) return;
+  ProfileEntry e; e.kind = kind;
+  if (cudaEventCreate(&e.start) != cudaSuccess || cudaEventCreate(&e.stop) != cudaSuccess) return;
+  cudaEventRecord(e.start, stream);
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  g_profile.push_back(e); slot = int(g_profile.size()) - 1;
+}
+ProfileScope::~ProfileScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  cudaEventRecord(g_profile[slot].stop, stream);
+}
 
 void timer_mark(const hyacinHandle_t* handle, Segment seg) {
   auto* t = static_cast<SegmentTimer*>(handle->timer);
@@ -129,4 +157,29 @@ extern "C" void hyacinSync_TimerSegments(const hyacinHandle_t* handle, double* e
   }
   for (auto& ev : t->events) cudaEventDestroy(ev.second);
   t->events.clear(); t->current = Segment::Untimed;
+}
+
+// ---- B200-only accounting entry points ------------------------------------------------------------------
+extern "C" int64_t hyacinB200LaunchCount(int32_t reset) {
+  return reset ? g_launches.exchange(0) : g_launches.load();
+}
+
+extern "C" void hyacinB200ProfileEnable(int32_t enable) {
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  for (auto& e : g_profile) { cudaEventDestroy(e.start); cudaEventDestroy(e.stop); }
+  g_profile.clear();
+  g_profile_on.store(enable ? 1 : 0);
+}
+
+extern "C" void hyacinB200ProfileRead(double* gramMs, int32_t* gramLaunches, double* quantizeMs, int32_t* quantizeLaunches) {
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  double ms[3] = {0., 0., 0.}; int n[3] = {0, 0, 0};
+  for (auto& e : g_profile) {
+    float t = 0.f;
+    if (cudaEventSynchronize(e.stop) == cudaSuccess && cudaEventElapsedTime(&t, e.start, e.stop) == cudaSuccess) { ms[int(e.kind)] += t; n[int(e.kind)] += 1; }
+    cudaEventDestroy(e.start); cudaEventDestroy(e.stop);
+  }
+  g_profile.clear();
+  if (gramMs) *gramMs = ms[int(KernelKind::Gram)]; if (gramLaunches) *gramLaunches = n[int(KernelKind::Gram)];
+  if (quantizeMs) *quantizeMs = ms[int(KernelKind::Quantize)]; if (quantizeLaunches) *quantizeLaunches = n[int(KernelKind::Quantize)];
 }

@@ -23,6 +23,16 @@ uint32_t* status_word_device(int device);
 uint32_t status_word_read(int device, bool clear);
 void status_check(const hyacinHandle_t* handle, const char* where);
 
+// Launch accounting: every kernel launch of this library is counted; with profiling switched on the Gram and
+// quantise launches are also bracketed by CUDA events on the launching stream (read back by hyacinB200Profile*).
+enum class KernelKind : int { Other = 0, Quantize = 1, Gram = 2 };
+void count_launch(int n = 1);
+struct ProfileScope {                       // RAII: records start/stop events around one launch when enabled
+  ProfileScope(cudaStream_t stream, KernelKind kind);
+  ~ProfileScope();
+  cudaStream_t stream; int slot;
+};
+
 // Timer classes of hyacinSync_TimerSegments ('D', 'R', 'C'; anything else untimed).
 enum class Segment : unsigned char { Untimed, Distributed, Replicated, Comm };
 void timer_mark(const hyacinHandle_t* handle, Segment seg);

@@ -245,6 +245,7 @@ int run_potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, const v
   double eps_sq = eps * eps;
   const E* g = static_cast<const E*>(G); E* rw = static_cast<E*>(Rw);
   void* args[] = {&eps_sq, &n, &cap, &g, &ldg, &rw, &D, &pos, &jpiv, &partials, &rank_host};
+  count_launch();
   HYB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(potrfp_kernel<R, CPLX>), dim3(grid), dim3(kBlock), args, 0, stream));
   HYB_CUDA(cudaFreeAsync(D, stream)); HYB_CUDA(cudaFreeAsync(pos, stream)); HYB_CUDA(cudaFreeAsync(partials, stream));
   HYB_CUDA(cudaStreamSynchronize(stream));

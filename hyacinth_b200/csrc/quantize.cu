@@ -135,6 +135,8 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
   p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;
   p.part_pitch = ldk; p.col_pitch = ldk * (cplx ? 3 : 1); p.plane_pitch = p.col_pitch * n;
   p.rows = rows; p.ldk = int(ldk); p.n = n; p.moduli = plan.moduli; p.value_bytes = plan.value_bytes;
+  ProfileScope prof(stream, KernelKind::Quantize);
+  count_launch();
   switch (int(atype)) {
     case HYACIN_F64: launch_typed<double, 1>(stream, p); break;
     case HYACIN_F32: launch_typed<float, 1>(stream, p); break;

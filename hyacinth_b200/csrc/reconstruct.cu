@@ -146,6 +146,7 @@ void launch_reconstruct(cudaStream_t stream, int n, int moduli, const uint8_t* r
                         uint64_t* C_panel) {
   if (n <= 0 || moduli <= 0 || order <= 0) return;
   const TilePlan tp = make_tile_plan(n);
+  count_launch();
   if (moduli <= 8) {
     dim3 grid(tp.num_tiles, kTileX / 32);
     reconstruct_kernel<8, 32><<<grid, kTileY, 0, stream>>>(n, moduli, tp.tiles_y, tp.num_tiles, residues, beta, order, C_panel);

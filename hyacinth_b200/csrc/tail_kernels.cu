@@ -142,6 +142,7 @@ __global__ void find_rank_kernel(double eps_sq, int n, int K, const R* __restric
 void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecision_t src_type, const void* src, int64_t lds,
                   hyacinPrecision_t dst_type, void* dst, int64_t ldd) {
   if (rows <= 0 || cols <= 0) return;
+  count_launch();
   const int cplx = is_complex(src_type);
   switch (base_type(src_type)) {
     case HYACIN_F64: dispatch_dst<double>(stream, op, rows, cols, cplx, src, lds, base_type(dst_type), dst, ldd); break;
@@ -155,6 +156,7 @@ void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecis
 void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, hyacinPrecision_t dst_type,
                        void* A, int64_t lda) {
   if (n <= 0 || rank <= 0) return;
+  count_launch();
   dim3 grid((n + 255) / 256, rank);
 #define ARGS(S, D) n, rank, static_cast<const S*>(Rw), static_cast<D*>(A), lda
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
@@ -180,6 +182,7 @@ void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t g
 void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, const int32_t* jpiv,
                        hyacinPrecision_t dst_type, void* B, int64_t ldb) {
   if (n <= 0 || rank <= 0) return;
+  count_launch();
   dim3 grid((rank + 255) / 256, n);
 #define ARGS(S, D) n, rank, static_cast<const S*>(Rw), jpiv, static_cast<D*>(B), ldb
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
@@ -205,6 +208,7 @@ void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t g
 void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, hyacinPrecision_t b_type, const void* B, int64_t ldb,
                     hyacinPrecision_t xtype, void* X, int64_t ldx) {
   if (n <= 0 || rank <= 0) return;
+  count_launch();
   dim3 grid((rank + 255) / 256, n);
   const int cplx = is_complex(xtype);
 #define RUN(S, D) do { if (cplx) interp_scatter_kernel<S, D, 2><<<grid, 256, 0, stream>>>(n, rank, jpiv, static_cast<const S*>(B), ldb, static_cast<D*>(X), ldx); \
@@ -223,6 +227,7 @@ void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, h
 void find_rank(cudaStream_t stream, double eps_sq, int n, int K, hyacinPrecision_t sigma_type, const void* sigma, hyacinPrecision_t out_type,
                void* out, int32_t* rank, double* suffix) {
   const bool s64 = base_type(sigma_type) == HYACIN_F64;
+  count_launch();
 #define RUN(R, S) find_rank_kernel<R, S><<<1, 256, 0, stream>>>(eps_sq, n, K, static_cast<const R*>(sigma), static_cast<S*>(out), rank, suffix)
   switch (base_type(out_type)) {
     case HYACIN_F64: if (s64) RUN(double, double); else RUN(float, double); break;

@@ -50,6 +50,23 @@ void hyacinB200GramResidues(const hyacinHandle_t* handle, int32_t N, int32_t mod
 void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const uint8_t* residues,
                            int32_t beta, int32_t orderC, uint64_t* Cpanel);
 
+/* Wire format of hyacinAllReduce1Drow for a value of orderA 63-bit limbs summed over `ranks` ranks: the value
+ * is cut into `slices` words, the first slices-1 holding widthBits unsigned bits each and the last the signed
+ * remainder, so that a plain unsigned 64-bit sum over all ranks cannot overflow.  Host only.
+ * Takes over the role of the reference's table of limb counts (src/allreduce_1drow.cu:151). */
+void hyacinB200SlicePlan(int32_t orderA, int32_t ranks, int32_t* slices, int32_t* widthBits);
+
+/* Number of kernels this library has launched in the calling process (optionally reset to zero).
+ * No counterpart in the reference. */
+int64_t hyacinB200LaunchCount(int32_t reset);
+
+/* In-situ kernel timing: while enabled, every quantise and Gram launch is bracketed by CUDA events on its own
+ * stream; hyacinB200ProfileRead waits for them, returns total milliseconds and launch counts per kind, and
+ * clears the record.  Enabling or disabling also clears it.  No counterpart in the reference (its timer,
+ * hyacinSync_TimerSegments, groups work by class, not by kernel). */
+void hyacinB200ProfileEnable(int32_t enable);
+void hyacinB200ProfileRead(double* gramMs, int32_t* gramLaunches, double* quantizeMs, int32_t* quantizeLaunches);
+
 #ifdef __cplusplus
 }
 #endif
