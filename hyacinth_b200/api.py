@@ -30,7 +30,7 @@ PUBLIC_SYMBOLS = [
 B200_SYMBOLS = [
     "hyacinB200Status", "hyacinB200CrtPlan", "hyacinB200TileInfo", "hyacinB200QuantizeCrt",
     "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
-    "hyacinB200ProfileRead", "hyacinB200SlicePlan",
+    "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic",
 ]
 
 
@@ -80,6 +80,7 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200GramResidues": (None, [H, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp]),
         "hyacinB200Reconstruct": (None, [H, i32, i32, vp, i32, i32, vp]),
         "hyacinB200SlicePlan": (None, [i32, i32, POINTER(i32), POINTER(i32)]),
+        "hyacinB200HerkBatchStatic": (i32, [H, i32, i32, i32, i32, i32, vp, i32, i32, vp, i32, i32, vp]),
         "hyacinB200LaunchCount": (i64, [i32]),
         "hyacinB200ProfileEnable": (None, [i32]),
         "hyacinB200ProfileRead": (None, [POINTER(f64), POINTER(i32), POINTER(f64), POINTER(i32)]),
@@ -148,6 +149,11 @@ class Hyacin:
 
     def herk_batch(self, batches, seg_m, last_m, n, atype, A, lda, u, vexp, beta, order_c, C):
         self.lib.hyacinXherkBatch(byref(self.h), batches, seg_m, last_m, n, atype, _dp(A), lda, u, _dp(vexp), beta, order_c, _dp(C))
+
+    def herk_batch_static(self, batches, seg_m, last_m, n, atype, A, lda, u, vexp, beta, order_c, C) -> int:
+        """hyacinXherkBatch with all scratch in the module's fixed array (no allocation); 0 on success."""
+        return int(self.lib.hyacinB200HerkBatchStatic(byref(self.h), batches, seg_m, last_m, n, atype, _dp(A), lda, u, _dp(vexp),
+                                                     beta, order_c, _dp(C)))
 
     def allreduce_vexp(self, n, vexp):
         self.lib.hyacinAllReduceVExp(byref(self.h), n, _dp(vexp))

@@ -51,6 +51,7 @@ uint32_t* status_word_device(int device) {
   }
   return g_status_dev[device];
 }
+uint32_t* status_word_if_ready(int device) { return (device >= 0 && device < 64) ? g_status_dev[device] : nullptr; }
 uint32_t status_word_read(int device, bool clear) {
   if (device < 0 || device >= 64 || !g_status_host[device]) return 0;
   volatile uint32_t* p = g_status_host[device]; uint32_t v = *p; if (clear) *p = 0; return v;

@@ -20,6 +20,7 @@ inline int base_type(hyacinPrecision_t t) { return int(t) & ~1; }
 
 // Status word of the bounded waits in the Gram kernel (pinned host memory mapped into the device).
 uint32_t* status_word_device(int device);
+uint32_t* status_word_if_ready(int device);      // never allocates: nullptr until status_word_device has run
 uint32_t status_word_read(int device, bool clear);
 void status_check(const hyacinHandle_t* handle, const char* where);
 

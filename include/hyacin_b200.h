@@ -50,6 +50,20 @@ void hyacinB200GramResidues(const hyacinHandle_t* handle, int32_t N, int32_t mod
 void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const uint8_t* residues,
                            int32_t beta, int32_t orderC, uint64_t* Cpanel);
 
+/* hyacinXherkBatch for callers that cannot allocate: same arguments, same exact integer Gram in C, but all
+ * scratch (int8 residue planes, residue accumulators) lives in a fixed 64 MiB array that is part of the loaded
+ * module instead of coming from handle->mempool.  It is meant for hosts that have handed the whole device to
+ * their own arena, or that call from a latency-bound loop where an allocator call is not acceptable.
+ * Returns 0 on success, -1 for unsupported arguments, -2 (with a message on stderr) when
+ * residues(N, moduli) + one 128-row chunk of planes exceed the array -- roughly N > 2000 for FP64 at eps 1e-10 --
+ * and -3 if the array's device address could not be obtained.  The first call on a device looks that address
+ * up and should be made outside any stream capture.  Calls on one device share the array: keep them on one
+ * stream or order them with events; calls whose kernels overlap on the GPU race.
+ * This entry point has no counterpart in the reference, whose hyacinXherkBatch always allocates from the pool. */
+int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32_t batches, int32_t segM, int32_t lastM, int32_t N,
+                                  hyacinPrecision_t Atype, const void* A, int32_t lda, int32_t u, const int32_t* vexp,
+                                  int32_t beta, int32_t orderC, uint64_t* C);
+
 /* Wire format of hyacinAllReduce1Drow for a value of orderA 63-bit limbs summed over `ranks` ranks: the value
  * is cut into `slices` words, the first slices-1 holding widthBits unsigned bits each and the last the signed
  * remainder, so that a plain unsigned 64-bit sum over all ranks cannot overflow.  Host only.
