@@ -8,8 +8,8 @@
 // How the residue is formed (new): q is biased by 2^(8 nb - 1) so that its nb bytes are unsigned; then
 //   q + 128 = bias_m + sum_b byte_b * (256^b mod m)   (mod m)
 // is one dp4a per four bytes, and the sum (< 2^20) is reduced with a single exact multiply-high.
-// Each thread converts four consecutive rows of one column and stores one 32-bit word per plane, so loads
-// and stores of a warp are contiguous 1 KiB / 128 B runs.
+// Each thread converts eight consecutive rows of one column and stores one 64-bit word per plane, so loads
+// and stores of a warp are contiguous 2 KiB / 256 B runs.
 #include "hyb_internal.h"
 #include "crt_tables.h"
 #include <cuda_fp16.h>
@@ -44,16 +44,6 @@ template <> __device__ __forceinline__ double load_as_double<__half>(const __hal
 
 __device__ __forceinline__ double pow2(int e) { return __longlong_as_double((long long)(e + 1023) << 52); }
 
-// Residue words of one biased value (up to three 32-bit words of bytes) for modulus i, in [0, m).
-template <int NW>
-__device__ __forceinline__ uint32_t residue(const QuantConsts& k, const uint32_t (&w)[3], int i) {
-  uint32_t t = k.bias[i];
-  t = __dp4a(w[0], k.weight[i][0], t);
-  if (NW > 1) t = __dp4a(w[1], k.weight[i][1], t);
-  if (NW > 2) t = __dp4a(w[2], k.weight[i][2], t);
-  return t - __umulhi(t, k.magic[i]) * k.modulus[i];
-}
-
 // rint(v) biased by 2^(8 nb - 1), as little-endian 32-bit words.  |v| <= 2^80.
 template <int NW>
 __device__ __forceinline__ void biased_words(double v, int value_bytes, bool negate, uint32_t (&w)[3]) {
@@ -75,12 +65,36 @@ __device__ __forceinline__ void biased_words(double v, int value_bytes, bool neg
   }
 }
 
-// grid.x covers ldk / (4 * blockDim.x) row groups, grid.y = columns.
+// grid.x covers ldk / (kRows * blockDim.x) row groups, grid.y = columns.
 // PARTS = 1: real input.  PARTS = 3: complex input -> planes (re, im, -re) stacked along K in each column.
+// Each thread converts kRows = 8 consecutive rows of one column: the per-modulus constants are fetched once per
+// eight values, the loads are 16-byte vectors when the column is 16-byte aligned, and every plane receives one
+// 8-byte store per thread (256 contiguous bytes per warp).
+constexpr int kRows = 8;
+
+template <typename T, int PARTS>
+__device__ __forceinline__ void load_rows(const T* __restrict__ src, int valid, double s1, double s2, double (&v)[kRows][PARTS == 1 ? 1 : 2]) {
+  constexpr int kReal = PARTS == 1 ? 1 : 2;
+  constexpr int kCount = kRows * kReal;                 // scalars this thread reads
+  constexpr int kVec = 16 / int(sizeof(T));             // scalars per 16-byte vector
+  T raw[kCount];
+  if (valid == kRows && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && kCount % kVec == 0) {
+#pragma unroll
+    for (int q = 0; q < kCount / kVec; ++q) reinterpret_cast<uint4*>(raw)[q] = __ldg(reinterpret_cast<const uint4*>(src) + q);
+  } else {
+#pragma unroll
+    for (int q = 0; q < kCount; ++q) raw[q] = (q / kReal) < valid ? src[q] : T(0);
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int c = 0; c < kReal; ++c) v[r][c] = (load_as_double<T>(&raw[r * kReal + c]) * s1) * s2;
+}
+
 template <typename T, int NW, int PARTS>
 __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
   const int col = blockIdx.y;
-  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kRows;
   if (row0 >= p.ldk) return;
   const int expon = p.vexp[col];
   // a * 2^expon as two exact scalings: the halves stay representable for every admissible exponent, and a
@@ -89,32 +103,41 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
   if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
   constexpr int kReal = PARTS == 1 ? 1 : 2;
   const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0) * kReal;
-  double v[4][kReal];
-#pragma unroll
-  for (int r = 0; r < 4; ++r)
-#pragma unroll
-    for (int c = 0; c < kReal; ++c)
-      v[r][c] = (row0 + r < p.rows) ? (load_as_double<T>(src + r * kReal + c) * s1) * s2 : 0.0;
+  int valid = p.rows - row0; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
+  double v[kRows][kReal];
+  load_rows<T, PARTS>(src, valid, s1, s2, v);
 
   int8_t* dst = p.W + int64_t(col) * p.col_pitch + row0;
 #pragma unroll
   for (int part = 0; part < PARTS; ++part) {
-    uint32_t w[4][3];
+    uint32_t w[kRows][3];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) biased_words<NW>(v[r][part == 1 ? 1 : 0], p.value_bytes, part == 2, w[r]);
+    for (int r = 0; r < kRows; ++r) biased_words<NW>(v[r][part == 1 ? 1 : 0], p.value_bytes, part == 2, w[r]);
     int8_t* out = dst + int64_t(part) * p.part_pitch;
 #pragma unroll 1
     for (int i = 0; i < p.moduli; ++i) {
-      uint32_t packed = residue<NW>(p.k, w[0], i) | (residue<NW>(p.k, w[1], i) << 8) |
-                        (residue<NW>(p.k, w[2], i) << 16) | (residue<NW>(p.k, w[3], i) << 24);
-      *reinterpret_cast<uint32_t*>(out + int64_t(i) * p.plane_pitch) = packed ^ 0x80808080u;   // subtract 128 per byte
+      const uint32_t bias = p.k.bias[i], w0 = p.k.weight[i][0], w1 = p.k.weight[i][1], w2 = p.k.weight[i][2];
+      const uint32_t magic = p.k.magic[i], modulus = p.k.modulus[i];
+      uint32_t r8[kRows];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        uint32_t t = __dp4a(w[r][0], w0, bias);
+        if (NW > 1) t = __dp4a(w[r][1], w1, t);
+        if (NW > 2) t = __dp4a(w[r][2], w2, t);
+        r8[r] = t - __umulhi(t, magic) * modulus;                       // exact: t * modulus < 2^32
+      }
+      // four residues per word by byte permutes (ALU pipe), then -128 per byte
+      uint2 packed;
+      packed.x = __byte_perm(__byte_perm(r8[0], r8[1], 0x0040), __byte_perm(r8[2], r8[3], 0x0040), 0x5410) ^ 0x80808080u;
+      packed.y = __byte_perm(__byte_perm(r8[4], r8[5], 0x0040), __byte_perm(r8[6], r8[7], 0x0040), 0x5410) ^ 0x80808080u;
+      *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch) = packed;
     }
   }
 }
 
 template <typename T, int PARTS>
 void launch_typed(cudaStream_t stream, const QuantParams& p) {
-  dim3 grid(unsigned((p.ldk / 4 + 255) / 256), unsigned(p.n));
+  dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
   const int nw = (p.value_bytes + 3) / 4;
   if (nw <= 1) quantize_crt_kernel<T, 1, PARTS><<<grid, 256, 0, stream>>>(p);
   else if (nw == 2) quantize_crt_kernel<T, 2, PARTS><<<grid, 256, 0, stream>>>(p);
