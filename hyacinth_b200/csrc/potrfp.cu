@@ -98,7 +98,6 @@ template <typename R, bool CPLX> struct Ops {
 
 constexpr int kBlock = 512;               // 16 warps: 32 columns per block, previous rows split 16 ways
 constexpr int kWarps = kBlock / 32;
-constexpr int kChunk = 256;               // previous rows staged per shared-memory pass
 
 template <typename R, bool CPLX>
 struct Partial { R val; double trace; int idx; int pad; };
@@ -113,6 +112,7 @@ potrfp_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restrict__ G
               int32_t* __restrict__ rank_out) {
   using E = Elem<R, CPLX>; using O = Ops<R, CPLX>; using T = Real<R>; using P = Partial<R, CPLX>;
   cg::grid_group grid = cg::this_grid();
+  constexpr int kChunk = sizeof(E) >= 32 ? 512 : 1024;   // previous rows staged per shared-memory pass
   __shared__ E s_pivot_row[kChunk];                 // conj-multiplier: previous rows at the pivot column
   __shared__ E s_partial[kWarps][32];
   __shared__ P s_red[kWarps];
@@ -153,17 +153,32 @@ potrfp_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restrict__ G
   for (;; ++k) {
     // ---- every block reduces the partials of all blocks in the same order: same pivot everywhere ----
     const P* cur = partials + size_t(k & 1) * nblocks;
-    if (threadIdx.x == 0) {
-      // volatile reads: these words are rewritten by other blocks every second step
-      const volatile P* vc = cur;
-      P acc; acc.trace = 0.; acc.idx = -1; acc.val = T::zero(); acc.pad = 0;
-      for (int b = 0; b < nblocks; ++b) {
-        P o; o.trace = vc[b].trace; o.idx = vc[b].idx;
-        if constexpr (sizeof(R) == 16) { o.val.x = vc[b].val.x; o.val.y = vc[b].val.y; } else o.val = vc[b].val;
-        acc.trace += o.trace;
-        if (o.idx >= 0 && (acc.idx < 0 || T::less(acc.val, o.val))) { acc.val = o.val; acc.idx = o.idx; }
+    {
+      // all threads take part: thread b fetches the partial of block b (L2 loads, these words are rewritten by
+      // other blocks every second step), then a fixed-shape tree reduces them -- same tree, same answer, in
+      // every block
+      P mine; mine.trace = 0.; mine.idx = -1; mine.val = T::zero(); mine.pad = 0;
+      for (int b = threadIdx.x; b < nblocks; b += kBlock) {
+        P o; o.trace = __ldcg(&cur[b].trace); o.idx = __ldcg(&cur[b].idx);
+        if constexpr (sizeof(R) == 16) { o.val.x = __ldcg(&cur[b].val.x); o.val.y = __ldcg(&cur[b].val.y); } else o.val = __ldcg(&cur[b].val);
+        mine.trace += o.trace;
+        if (o.idx >= 0 && (mine.idx < 0 || T::less(mine.val, o.val))) { mine.val = o.val; mine.idx = o.idx; }
       }
-      s_best = acc;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        P other; other.trace = __shfl_down_sync(0xffffffffu, mine.trace, o); other.idx = __shfl_down_sync(0xffffffffu, mine.idx, o);
+        if constexpr (sizeof(R) == 16) { other.val.x = __shfl_down_sync(0xffffffffu, mine.val.x, o); other.val.y = __shfl_down_sync(0xffffffffu, mine.val.y, o); }
+        else other.val = __shfl_down_sync(0xffffffffu, mine.val, o);
+        mine.trace += other.trace;
+        if (other.idx >= 0 && (mine.idx < 0 || T::less(mine.val, other.val))) { mine.val = other.val; mine.idx = other.idx; }
+      }
+      if (lane == 0) s_red[warp] = mine;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        P acc = s_red[0];
+        for (int w = 1; w < kWarps; ++w) { acc.trace += s_red[w].trace; if (s_red[w].idx >= 0 && (acc.idx < 0 || T::less(acc.val, s_red[w].val))) { acc.val = s_red[w].val; acc.idx = s_red[w].idx; } }
+        s_best = acc;
+      }
     }
     __syncthreads();
     const P best = s_best;
@@ -179,14 +194,35 @@ potrfp_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restrict__ G
     for (int c0 = blockIdx.x * 32; c0 < n; c0 += nblocks * 32) {
       const int i = c0 + lane;
       const bool live = i < n && i != p && __ldcg(&pos[i]) >= k;
-      E acc = O::zero();
+      // kUnroll independent accumulators per thread and kUnroll row loads in flight before any is consumed: the
+      // step is bound by the latency of these loads (the factor rows live in L2 / HBM), not by arithmetic
+      constexpr int kUnroll = sizeof(E) >= 32 ? 4 : 8;
+      E accs[kUnroll];
+#pragma unroll
+      for (int q = 0; q < kUnroll; ++q) accs[q] = O::zero();
       for (int l0 = 0; l0 < k; l0 += kChunk) {
         const int lc = min(kChunk, k - l0);
         __syncthreads();
         for (int t = threadIdx.x; t < lc; t += kBlock) s_pivot_row[t] = Rw[size_t(l0 + t) * n + p];
         __syncthreads();
-        if (live) for (int t = warp; t < lc; t += kWarps) acc = O::sub_conj_mul(acc, s_pivot_row[t], Rw[size_t(l0 + t) * n + i]);
+        if (live) {
+          const E* base = Rw + size_t(l0) * n + i;
+          int t = warp;
+          for (; t + (kUnroll - 1) * kWarps < lc; t += kUnroll * kWarps) {
+            E rows[kUnroll];
+#pragma unroll
+            for (int q = 0; q < kUnroll; ++q) rows[q] = base[size_t(t + q * kWarps) * n];
+#pragma unroll
+            for (int q = 0; q < kUnroll; ++q) accs[q] = O::sub_conj_mul(accs[q], s_pivot_row[t + q * kWarps], rows[q]);
+          }
+          for (; t < lc; t += kWarps) accs[0] = O::sub_conj_mul(accs[0], s_pivot_row[t], base[size_t(t) * n]);
+        }
       }
+#pragma unroll
+      for (int q = kUnroll / 2; q > 0; q >>= 1)
+#pragma unroll
+        for (int r = 0; r < q; ++r) accs[r] = O::add(accs[r], accs[r + q]);
+      const E acc = accs[0];
       s_partial[warp][lane] = acc;
       __syncthreads();
       if (warp == 0) {
