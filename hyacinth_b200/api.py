@@ -30,7 +30,7 @@ PUBLIC_SYMBOLS = [
 B200_SYMBOLS = [
     "hyacinB200Status", "hyacinB200CrtPlan", "hyacinB200TileInfo", "hyacinB200QuantizeCrt",
     "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
-    "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic",
+    "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic", "hyacinB200QuantizeLimbs", "hyacinB200GramLimbs",
 ]
 
 
@@ -81,6 +81,8 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200Reconstruct": (None, [H, i32, i32, vp, i32, i32, vp]),
         "hyacinB200SlicePlan": (None, [i32, i32, POINTER(i32), POINTER(i32)]),
         "hyacinB200HerkBatchStatic": (i32, [H, i32, i32, i32, i32, i32, vp, i32, i32, vp, i32, i32, vp]),
+        "hyacinB200QuantizeLimbs": (None, [H, i32, i32, i32, vp, i32, vp, i32, vp, i64]),
+        "hyacinB200GramLimbs": (None, [H, i32, i32, vp, i64, i64, i32, i32, i32, i32, i32, vp]),
         "hyacinB200LaunchCount": (i64, [i32]),
         "hyacinB200ProfileEnable": (None, [i32]),
         "hyacinB200ProfileRead": (None, [POINTER(f64), POINTER(i32), POINTER(f64), POINTER(i32)]),
@@ -222,6 +224,12 @@ class Hyacin:
 
     def gram_residues(self, n, moduli, W, ldw, plane_stride, ka0, kb0, k_rows, accumulate, residues):
         self.lib.hyacinB200GramResidues(byref(self.h), n, moduli, _dp(W), ldw, plane_stride, ka0, kb0, k_rows, accumulate, _dp(residues))
+
+    def quantize_limbs(self, atype, rows, n, A, lda, vexp, order, W, ldk):
+        self.lib.hyacinB200QuantizeLimbs(byref(self.h), atype, rows, n, _dp(A), lda, _dp(vexp), order, _dp(W), ldk)
+
+    def gram_limbs(self, n, order, W, ldw, plane_stride, ka0, kb0, k_rows, beta, order_c, C):
+        self.lib.hyacinB200GramLimbs(byref(self.h), n, order, _dp(W), ldw, plane_stride, ka0, kb0, k_rows, beta, order_c, _dp(C))
 
     def reconstruct(self, n, moduli, residues, beta, order_c, C):
         self.lib.hyacinB200Reconstruct(byref(self.h), n, moduli, _dp(residues), beta, order_c, _dp(C))

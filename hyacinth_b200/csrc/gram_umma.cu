@@ -18,6 +18,7 @@
 // status word for the host and makes all roles leave their loops so that TMEM is still released.
 #include "hyb_internal.h"
 #include "crt_tables.h"
+#include "limbs192.cuh"
 #include <cuda.h>
 #include <mutex>
 
@@ -46,6 +47,9 @@ struct GramParams {
   int ka0, kb0;                 // first K row of the A / B operand inside a column
   int num_kblocks;              // k_rows / kStageK
   int num_tiles, tiles_y, moduli, accumulate;
+  // limb mode: planes are the balanced base-256 digits of the quantised values; the accumulator of shift s
+  // collects every digit pair (i, j) with i + j = s and is added to the packed integer Gram at bit 8 s
+  uint64_t* gram; int64_t tri; int n, order, limb_panels, overwrite;
   ModConsts k;
 };
 
@@ -134,8 +138,13 @@ struct Barriers {
   uint32_t tmem_base; uint32_t abort_flag;
 };
 
+// LIMBS = false: one work group per (modulus, tile), one accumulator, epilogue = residue bytes.
+// LIMBS = true : one work group per tile, 2 order - 1 accumulators (one per shift) handled one after the other by
+//                the same CTA, epilogue = read-modify-write of the packed 63-bit limbs (the same thread owns an
+//                entry for every shift, so no atomics are needed).
+template <bool LIMBS>
 __global__ void __launch_bounds__(kThreads, 1)
-gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p) {
+gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;                 // swizzle atoms need 1 KiB alignment
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -143,7 +152,8 @@ gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_items = p.moduli * p.num_tiles;
+  const int num_groups = LIMBS ? p.num_tiles : p.moduli * p.num_tiles;
+  const int subs = LIMBS ? 2 * p.order - 1 : 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -161,16 +171,24 @@ gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0; bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int m = item / p.num_tiles; int ty, tx; tile_coords(p.tiles_y, item % p.num_tiles, &ty, &tx);
-        for (int kb = 0; kb < p.num_kblocks; ++kb) {
-          if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 1u))) break;
-          mbar_expect_tx(&bars->full[stage], kStageBytes);
-          const uint32_t sa = base + stage * kStageBytes, sb = sa + kABytes;
-          tma_load_3d(sa, &tmap, &bars->full[stage], p.ka0 + kb * kStageK, ty * kTileY, m);
-          tma_load_3d(sb, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX, m);
-          tma_load_3d(sb + kABytes, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX + kTileY, m);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x) {
+        int ty, tx; tile_coords(p.tiles_y, LIMBS ? group : group % p.num_tiles, &ty, &tx);
+        for (int sub = 0; sub < subs && ok; ++sub) {
+          // plane pairs of this accumulator: (m, m) for residues; (i, sub - i) for limbs
+          const int first = LIMBS ? (sub - (p.order - 1) > 0 ? sub - (p.order - 1) : 0) : group / p.num_tiles;
+          const int last = LIMBS ? (sub < p.order - 1 ? sub : p.order - 1) : first;
+          for (int pa = first; pa <= last && ok; ++pa) {
+            const int pb = LIMBS ? sub - pa : pa;
+            for (int kb = 0; kb < p.num_kblocks; ++kb) {
+              if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 1u))) break;
+              mbar_expect_tx(&bars->full[stage], kStageBytes);
+              const uint32_t sa = base + stage * kStageBytes, sb = sa + kABytes;
+              tma_load_3d(sa, &tmap, &bars->full[stage], p.ka0 + kb * kStageK, ty * kTileY, pa);
+              tma_load_3d(sb, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX, pb);
+              tma_load_3d(sb + kABytes, &tmap, &bars->full[stage], p.kb0 + kb * kStageK, tx * kTileX + kTileY, pb);
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+          }
         }
       }
     }
@@ -178,11 +196,14 @@ gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0; bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x)
+      for (int sub = 0; sub < subs && ok; ++sub) {
         if (!(ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2u))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kTileX;
-        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+        const int pairs = LIMBS ? ((sub < p.order - 1 ? sub : p.order - 1) - (sub - (p.order - 1) > 0 ? sub - (p.order - 1) : 0) + 1) : 1;
+        const int total_kb = pairs * p.num_kblocks;
+        for (int kb = 0; kb < total_kb; ++kb) {
           if (!(ok = mbar_wait(&bars->full[stage], phase, abort_flag, p.status, 3u))) break;
           tc_fence_after();
           const uint32_t sa = base + stage * kStageBytes, sb = sa + kABytes;
@@ -205,15 +226,38 @@ gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
     const int lane_group = warp & 3;                     // TMEM lanes 32 * (warp % 4) .. +31 are visible to this warp
     const int row = lane_group * 32 + lane;
     uint32_t acc = 0, acc_phase = 0; bool ok = true;
-    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-      const int m = item / p.num_tiles, tile = item % p.num_tiles;
+    for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x)
+    for (int sub = 0; sub < subs && ok; ++sub) {
+      const int m = LIMBS ? 0 : group / p.num_tiles, tile = LIMBS ? group : group % p.num_tiles;
       ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status, 4u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
+      if constexpr (LIMBS) {
+        int ty, tx; tile_coords(p.tiles_y, tile, &ty, &tx);
+        const int y = ty * kTileY + row;
+        const bool store_only = p.overwrite && sub == 0;        // first shift of the first chunk of a beta = 0 call
+#pragma unroll 1
+        for (int c = 0; c < kTileX / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll 4
+          for (int q = 0; q < 32; ++q) {
+            const int x = tx * kTileX + c * 32 + q;
+            if (y < p.n && x < p.n && y <= x) {
+              uint64_t* dst = p.gram + y + (int64_t(x) * (x + 1)) / 2;
+              U192 acc192; acc192.w[0] = acc192.w[1] = acc192.w[2] = 0;
+              if (!store_only) acc192 = limbs_to_u192(dst, p.tri, p.limb_panels);
+              add_i32_shifted(acc192, int32_t(v[q]), 8 * sub);
+              store_limbs(acc192, dst, p.tri, p.limb_panels);
+            }
+          }
+        }
+      } else {
       const uint32_t modulus = p.k.modulus[m], magic = p.k.magic[m], bias = p.k.bias[m];
       uint8_t* out = p.residues + (size_t(m) * p.num_tiles + tile) * size_t(kTileY * kTileX) + size_t(row) * kTileX;
-      const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
 #pragma unroll 1
       for (int c = 0; c < kTileX / 32; ++c) {
         uint32_t v[32];
@@ -239,6 +283,7 @@ gram_residue_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_const
         }
         *reinterpret_cast<uint4*>(out + c * 32) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         *reinterpret_cast<uint4*>(out + c * 32 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -282,21 +327,27 @@ TilePlan make_tile_plan(int n) {
   return t;
 }
 
-void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
+namespace {
+bool encode_planes(CUtensorMap* tmap, const int8_t* w, int64_t ldw, int n, int planes, int64_t plane_stride) {
   EncodeTiledFn encode = encode_tiled();
-  if (!encode) return;
-  const TilePlan tp = make_tile_plan(g.n);
-  CUtensorMap tmap;
-  const cuuint64_t dims[3] = {cuuint64_t(g.ldw), cuuint64_t(g.n), cuuint64_t(g.moduli)};
-  const cuuint64_t strides[2] = {cuuint64_t(g.ldw), cuuint64_t(g.plane_stride)};
+  if (!encode) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(ldw), cuuint64_t(n), cuuint64_t(planes)};
+  const cuuint64_t strides[2] = {cuuint64_t(ldw), cuuint64_t(plane_stride)};
   const cuuint32_t box[3] = {cuuint32_t(kStageK), cuuint32_t(kTileY), 1};
   const cuuint32_t elem[3] = {1, 1, 1};
-  CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(g.w), dims, strides, box, elem,
+  CUresult r = encode(tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<int8_t*>(w), dims, strides, box, elem,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) { std::fprintf(stderr, "hyacin-b200: cuTensorMapEncodeTiled failed (%d)\n", int(r)); return; }
+  if (r != CUDA_SUCCESS) { std::fprintf(stderr, "hyacin-b200: cuTensorMapEncodeTiled failed (%d)\n", int(r)); return false; }
+  return true;
+}
+}  // namespace
 
-  GramParams p;
+void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
+  const TilePlan tp = make_tile_plan(g.n);
+  CUtensorMap tmap;
+  if (!encode_planes(&tmap, g.w, g.ldw, g.n, g.moduli, g.plane_stride)) return;
+  GramParams p{};
   p.residues = g.residues; p.status = g.status;
   p.ka0 = g.ka0; p.kb0 = g.kb0; p.num_kblocks = g.k_rows / kStageK;
   p.num_tiles = tp.num_tiles; p.tiles_y = tp.tiles_y; p.moduli = g.moduli; p.accumulate = g.accumulate;
@@ -305,13 +356,31 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
     p.k.modulus[i] = m; p.k.magic[i] = crt::kMagicFloor[i];
     p.k.bias[i] = (0x80000000u / m) * m;
   }
-  HYB_CUDA(cudaFuncSetAttribute(gram_residue_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+  HYB_CUDA(cudaFuncSetAttribute(gram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
   const int items = g.moduli * tp.num_tiles;
   int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > items) grid = items;
   if (grid <= 0 || p.num_kblocks <= 0) return;
   ProfileScope prof(stream, KernelKind::Gram);
   count_launch();
-  gram_residue_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+  gram_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+  HYB_CUDA(cudaGetLastError());
+}
+
+void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g) {
+  const TilePlan tp = make_tile_plan(g.n);
+  CUtensorMap tmap;
+  if (!encode_planes(&tmap, g.w, g.ldw, g.n, g.order, g.plane_stride)) return;
+  GramParams p{};
+  p.status = g.status; p.ka0 = g.ka0; p.kb0 = g.kb0; p.num_kblocks = g.k_rows / kStageK;
+  p.num_tiles = tp.num_tiles; p.tiles_y = tp.tiles_y;
+  p.gram = g.gram; p.tri = (int64_t(g.n) * g.n + g.n) / 2; p.n = g.n; p.order = g.order; p.limb_panels = g.limb_panels;
+  p.overwrite = g.overwrite;
+  HYB_CUDA(cudaFuncSetAttribute(gram_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+  int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > tp.num_tiles) grid = tp.num_tiles;
+  if (grid <= 0 || p.num_kblocks <= 0 || g.order <= 0) return;
+  ProfileScope prof(stream, KernelKind::Gram);
+  count_launch();
+  gram_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
   HYB_CUDA(cudaGetLastError());
 }
 

@@ -105,6 +105,51 @@ static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPr
                                    cplx ? "COMPLEX" : "REAL", n, (long long)rows, plan.moduli);
 }
 
+// Limb route: the quantised values are split into `order` balanced base-256 digits and every digit pair is
+// multiplied on the tensor cores; pairs with the same shift share a TMEM accumulator and the epilogue adds it
+// into the packed integer Gram at bit 8 (i + j).  order^2 tile products per row chunk against `moduli` for the
+// CRT route, so it is the cheaper one only for small bit budgets (and whenever the caller forces it).
+static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda,
+                       int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
+  cudaStream_t stream = handle->cudaStream;
+  const int cplx = is_complex(atype), parts = cplx ? 3 : 1, kmul = cplx ? 2 : 1;
+  const int order = (u + 9) / 8;
+  const int64_t tri = (int64_t(n) * n + n) / 2;
+  const size_t elem = (base_type(atype) == HYACIN_F64 ? 8 : base_type(atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);
+  // order * k_rows * 2^14 < 2^31 for the shared int32 accumulators (k_rows counts both stacked parts of a complex operand)
+  int64_t chunk = (131071 / (int64_t(order) * kmul)) / kStageK * kStageK;
+  chunk = std::min<int64_t>(chunk, (rows + kStageK - 1) / kStageK * kStageK);
+  int8_t* W = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&W), size_t(chunk) * parts * size_t(n) * order, handle->mempool, stream));
+  uint32_t* status = status_word_device(handle->DeviceID);
+  if (!W || !status) { if (W) cudaFreeAsync(W, stream); return; }
+  bool first = true;
+  for (int64_t c0 = 0; c0 < rows; c0 += chunk) {
+    const int rc = int(std::min<int64_t>(chunk, rows - c0));
+    const int64_t ldk = (rc + kStageK - 1) / kStageK * kStageK;
+    const char* src = static_cast<const char*>(A) + size_t(c0) * elem;
+    launch_quantize_limbs(stream, atype, rc, n, src, lda, vexp, order, W, ldk);
+    GramLimbLaunch gl{};
+    gl.w = W; gl.ldw = ldk * parts; gl.plane_stride = gl.ldw * n; gl.ka0 = 0; gl.kb0 = 0; gl.k_rows = int(ldk) * kmul;
+    gl.n = n; gl.order = order; gl.limb_panels = order_c; gl.overwrite = (first && beta == 0) ? 1 : 0;
+    gl.sm_count = handle->DeviceSMs; gl.gram = C; gl.status = status;
+    launch_gram_limbs(stream, gl);
+    if (cplx) { gl.kb0 = int(ldk); gl.gram = C + size_t(order_c) * tri; launch_gram_limbs(stream, gl); }
+    first = false;
+  }
+  HYB_CUDA(cudaFreeAsync(W, stream));
+  if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "I8I32-GEMM-%s [algo=TN,limbs,tcgen05] [M=N=%d] [K=%lld] [Order=%d]\n",
+                                   cplx ? "COMPLEX" : "REAL", n, (long long)rows, order);
+}
+
+// 'L' forces limbs, 'C' forces CRT; otherwise the route with fewer tile products per row chunk is taken.
+bool use_limb_route(char algorithm, int u, int cplx, int64_t rows) {
+  if (algorithm == 'L' || algorithm == 'l') return true;
+  if (algorithm == 'C' || algorithm == 'c') return false;
+  const int order = (u + 9) / 8;
+  return order * order < make_crt_plan(u, cplx, rows).moduli;
+}
+
 }  // namespace hyb
 
 extern "C" void hyacinXherkBatchInit(const hyacinHandle_t* handle, double eps, uint64_t M, int32_t N, hyacinPrecision_t Atype,
@@ -146,7 +191,8 @@ extern "C" void hyacinXherkBatch(const hyacinHandle_t* handle, int32_t batches, 
     }
     return;
   }
-  hyb::herk_crt(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
+  if (hyb::use_limb_route(handle->GramMatrixAlgorithm, u, cplx, rows)) hyb::herk_limbs(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
+  else hyb::herk_crt(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
 }
 
 extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
@@ -222,4 +268,25 @@ extern "C" void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, i
                                       int32_t orderC, uint64_t* Cpanel) {
   if (N <= 0 || moduli <= 0 || moduli > hyb::crt::kMaxModuli || orderC <= 0 || orderC > 3) return;
   hyb::launch_reconstruct(handle->cudaStream, N, moduli, residues, beta ? 1 : 0, orderC, Cpanel);
+}
+
+extern "C" void hyacinB200QuantizeLimbs(const hyacinHandle_t* handle, hyacinPrecision_t Atype, int32_t rows, int32_t N, const void* A,
+                                        int32_t lda, const int32_t* vexp, int32_t order, int8_t* W, int64_t ldk) {
+  if (N <= 0 || rows < 0 || order < 1 || order > hyb::crt::kMaxBytes || ldk % hyb::kStageK) return;
+  if (int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX)) return;
+  hyb::launch_quantize_limbs(handle->cudaStream, Atype, rows, N, A, lda, vexp, order, W, ldk);
+}
+
+extern "C" void hyacinB200GramLimbs(const hyacinHandle_t* handle, int32_t N, int32_t order, const int8_t* W, int64_t ldw,
+                                    int64_t planeStride, int32_t ka0, int32_t kb0, int32_t kRows, int32_t beta, int32_t orderC,
+                                    uint64_t* Cpanel) {
+  if (N <= 0 || order < 1 || order > hyb::crt::kMaxBytes || kRows <= 0 || orderC < 1 || orderC > 3) return;
+  if (kRows % hyb::kStageK || ka0 % hyb::kStageK || kb0 % hyb::kStageK || ldw % 16 || planeStride % 16) return;
+  if (int64_t(order) * kRows > 131071) return;
+  hyb::GramLimbLaunch g{};
+  g.w = W; g.ldw = ldw; g.plane_stride = planeStride; g.ka0 = ka0; g.kb0 = kb0; g.k_rows = kRows; g.n = N; g.order = order;
+  g.limb_panels = orderC; g.overwrite = beta ? 0 : 1; g.sm_count = handle->DeviceSMs; g.gram = Cpanel;
+  g.status = hyb::status_word_device(handle->DeviceID);
+  if (!g.status) return;
+  hyb::launch_gram_limbs(handle->cudaStream, g);
 }

@@ -107,6 +107,24 @@ struct GramLaunch {
 };
 void launch_gram_residues(cudaStream_t stream, const GramLaunch& g);
 
+// Limb Gram of one chunk, straight into the packed integer Gram (one panel: real or imaginary part):
+//   gram[y <= x] (+)= sum_{i, j < order} 2^(8 (i + j)) sum_{k < k_rows} W[i][y][ka0 + k] * W[j][x][kb0 + k]
+// W holds `order` planes of balanced base-256 digits.  order * k_rows * 2^14 must stay below 2^31 (digit pairs
+// with the same i + j share one int32 accumulator).  overwrite: the call defines gram instead of adding to it.
+// Reference counterpart: src/hyacin_herk.cpp:111-161 with src/limbs_diag.cu, limbs_cross_real.cu, limbs_cross_imag.cu.
+struct GramLimbLaunch {
+  const int8_t* w;
+  int64_t ldw, plane_stride;
+  int ka0, kb0, k_rows, n, order, limb_panels, overwrite, sm_count;
+  uint64_t* gram;
+  uint32_t* status;
+};
+void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g);
+// Quantise rows of A into `order` planes of balanced base-256 digits (same plane layout as launch_quantize_crt).
+// Reference counterpart: src/quantize_limbs.cu:29-79.
+void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
+                           const int32_t* vexp, int order, int8_t* W, int64_t ldk);
+
 // CRT reconstruction of `moduli` residue planes into the packed 63-bit-limb Gram:
 //   C[panel][order][tri] = (beta ? C : 0) + value.  Reference counterpart: src/crt_reconstruct_real.cu:51-92.
 void launch_reconstruct(cudaStream_t stream, int n, int moduli, const uint8_t* residues, int beta, int order,

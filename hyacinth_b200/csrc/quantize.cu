@@ -135,6 +135,77 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
   }
 }
 
+// ---- balanced base-256 digits ("limbs") --------------------------------------------------------------------
+// q + sum_k 128 * 256^k has unsigned bytes b_k with q = sum_k (b_k - 128) 256^k, so digit k is simply byte k with
+// its top bit flipped: no carries.  `order` digits hold every |q| <= 2^(8 order - 2).
+struct LimbParams {
+  const void* A; int64_t lda; const int32_t* vexp;
+  int8_t* W; int64_t col_pitch, plane_pitch, part_pitch;
+  int rows, ldk, n, order;
+};
+
+template <typename T, int NW, int PARTS>
+__global__ void __launch_bounds__(256) quantize_limbs_kernel(const __grid_constant__ LimbParams p) {
+  const int col = blockIdx.y;
+  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kRows;
+  if (row0 >= p.ldk) return;
+  const int expon = p.vexp[col];
+  double s1 = 0.0, s2 = 0.0;
+  if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+  constexpr int kReal = PARTS == 1 ? 1 : 2;
+  const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0) * kReal;
+  int valid = p.rows - row0; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
+  double v[kRows][kReal];
+  load_rows<T, PARTS>(src, valid, s1, s2, v);
+  // bias words: 0x80 in each of the `order` low bytes
+  uint32_t bias[3];
+#pragma unroll
+  for (int w = 0; w < 3; ++w) { const int nb = p.order - 4 * w; bias[w] = nb >= 4 ? 0x80808080u : (nb <= 0 ? 0u : (0x80808080u >> (8 * (4 - nb)))); }
+  int8_t* dst = p.W + int64_t(col) * p.col_pitch + row0;
+#pragma unroll
+  for (int part = 0; part < PARTS; ++part) {
+    uint32_t w[kRows][3];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const double x = v[r][part == 1 ? 1 : 0];
+      if (NW <= 2) {
+        long long q = __double2ll_rn(x); if (part == 2) q = -q;
+        const unsigned long long b = (unsigned long long)q + ((unsigned long long)bias[1] << 32 | bias[0]);
+        w[r][0] = uint32_t(b); w[r][1] = uint32_t(b >> 32); w[r][2] = 0;
+      } else {
+        __int128 q;
+        if (fabs(x) < 4611686018427387904.0) q = __double2ll_rn(x);
+        else { const double hi = trunc(x * 2.3283064365386963e-10), lo = x - hi * 4294967296.0; q = ((__int128)__double2ll_rn(hi) << 32) + (__int128)__double2ll_rn(lo); }
+        if (part == 2) q = -q;
+        const unsigned __int128 b = (unsigned __int128)q + (((unsigned __int128)bias[2] << 64) | ((unsigned __int128)bias[1] << 32) | bias[0]);
+        w[r][0] = uint32_t(b); w[r][1] = uint32_t(b >> 32); w[r][2] = uint32_t(b >> 64);
+      }
+    }
+    int8_t* out = dst + int64_t(part) * p.part_pitch;
+#pragma unroll
+    for (int k = 0; k < 4 * NW; ++k) {
+      if (k < p.order) {
+        uint32_t d[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) d[r] = w[r][k >> 2] >> (8 * (k & 3));
+        uint2 packed;
+        packed.x = __byte_perm(__byte_perm(d[0], d[1], 0x0040), __byte_perm(d[2], d[3], 0x0040), 0x5410) ^ 0x80808080u;
+        packed.y = __byte_perm(__byte_perm(d[4], d[5], 0x0040), __byte_perm(d[6], d[7], 0x0040), 0x5410) ^ 0x80808080u;
+        *reinterpret_cast<uint2*>(out + int64_t(k) * p.plane_pitch) = packed;
+      }
+    }
+  }
+}
+
+template <typename T, int PARTS>
+void launch_limbs_typed(cudaStream_t stream, const LimbParams& p) {
+  dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
+  const int nw = (p.order + 3) / 4;
+  if (nw <= 1) quantize_limbs_kernel<T, 1, PARTS><<<grid, 256, 0, stream>>>(p);
+  else if (nw == 2) quantize_limbs_kernel<T, 2, PARTS><<<grid, 256, 0, stream>>>(p);
+  else quantize_limbs_kernel<T, 3, PARTS><<<grid, 256, 0, stream>>>(p);
+}
+
 template <typename T, int PARTS>
 void launch_typed(cudaStream_t stream, const QuantParams& p) {
   dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
@@ -167,6 +238,28 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
     case HYACIN_F64_COMPLEX: launch_typed<double, 3>(stream, p); break;
     case HYACIN_F32_COMPLEX: launch_typed<float, 3>(stream, p); break;
     case HYACIN_F16_COMPLEX: launch_typed<__half, 3>(stream, p); break;
+    default: break;
+  }
+  HYB_CUDA(cudaGetLastError());
+}
+
+void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
+                           const int32_t* vexp, int order, int8_t* W, int64_t ldk) {
+  if (order < 1 || order > crt::kMaxBytes) return;
+  const int cplx = is_complex(atype);
+  LimbParams p;
+  p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;
+  p.part_pitch = ldk; p.col_pitch = ldk * (cplx ? 3 : 1); p.plane_pitch = p.col_pitch * n;
+  p.rows = rows; p.ldk = int(ldk); p.n = n; p.order = order;
+  ProfileScope prof(stream, KernelKind::Quantize);
+  count_launch();
+  switch (int(atype)) {
+    case HYACIN_F64: launch_limbs_typed<double, 1>(stream, p); break;
+    case HYACIN_F32: launch_limbs_typed<float, 1>(stream, p); break;
+    case HYACIN_F16: launch_limbs_typed<__half, 1>(stream, p); break;
+    case HYACIN_F64_COMPLEX: launch_limbs_typed<double, 3>(stream, p); break;
+    case HYACIN_F32_COMPLEX: launch_limbs_typed<float, 3>(stream, p); break;
+    case HYACIN_F16_COMPLEX: launch_limbs_typed<__half, 3>(stream, p); break;
     default: break;
   }
   HYB_CUDA(cudaGetLastError());

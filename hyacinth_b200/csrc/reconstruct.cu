@@ -15,6 +15,7 @@
 // the threads of a warp hold consecutive y, so every store instruction covers one contiguous run of C.
 #include "hyb_internal.h"
 #include "crt_tables.h"
+#include "limbs192.cuh"
 
 namespace hyb {
 namespace {
@@ -24,57 +25,6 @@ __constant__ uint32_t c_magic[crt::kMaxModuli] = HYB_CRT_MAGIC_CEIL_INIT;
 __constant__ uint8_t c_inv[crt::kMaxModuli][crt::kMaxModuli] = HYB_CRT_INV_INIT;
 __constant__ uint64_t c_product[crt::kMaxModuli][3] = HYB_CRT_PRODUCT_INIT;
 __constant__ uint64_t c_half_product[crt::kMaxModuli][3] = HYB_CRT_HALF_PRODUCT_INIT;
-
-struct U192 { uint64_t w[3]; };
-
-__device__ __forceinline__ void mul_small_add(U192& v, uint32_t m, uint32_t a) {
-  unsigned __int128 t = (unsigned __int128)v.w[0] * m + a; v.w[0] = uint64_t(t);
-  t = (unsigned __int128)v.w[1] * m + uint64_t(t >> 64); v.w[1] = uint64_t(t);
-  v.w[2] = v.w[2] * m + uint64_t(t >> 64);
-}
-__device__ __forceinline__ void add192(U192& v, const U192& o) {
-  unsigned __int128 t = (unsigned __int128)v.w[0] + o.w[0]; v.w[0] = uint64_t(t);
-  t = (unsigned __int128)v.w[1] + o.w[1] + uint64_t(t >> 64); v.w[1] = uint64_t(t);
-  v.w[2] = v.w[2] + o.w[2] + uint64_t(t >> 64);
-}
-__device__ __forceinline__ void sub192(U192& v, const uint64_t (&o)[3]) {
-  unsigned __int128 t = (unsigned __int128)v.w[0] - o[0]; v.w[0] = uint64_t(t);
-  uint64_t borrow = uint64_t(t >> 64) & 1u;
-  t = (unsigned __int128)v.w[1] - o[1] - borrow; v.w[1] = uint64_t(t);
-  borrow = uint64_t(t >> 64) & 1u;
-  v.w[2] = v.w[2] - o[2] - borrow;
-}
-__device__ __forceinline__ bool greater192(const U192& v, const uint64_t (&o)[3]) {   // unsigned v > o
-  if (v.w[2] != o[2]) return v.w[2] > o[2];
-  if (v.w[1] != o[1]) return v.w[1] > o[1];
-  return v.w[0] > o[0];
-}
-__device__ __forceinline__ void sar63(U192& v) {   // arithmetic shift right by 63 (two's complement)
-  const uint64_t ext = uint64_t(int64_t(v.w[2]) >> 63);
-  const uint64_t n0 = (v.w[0] >> 63) | (v.w[1] << 1), n1 = (v.w[1] >> 63) | (v.w[2] << 1), n2 = (v.w[2] >> 63) | (ext << 1);
-  v.w[0] = n0; v.w[1] = n1; v.w[2] = n2;
-}
-// 63-bit limbs (signed last limb) -> 192-bit two's complement.
-__device__ __forceinline__ U192 limbs_to_u192(const uint64_t* p, int64_t stride, int order) {
-  U192 v; const uint64_t a0 = p[0];
-  if (order == 1) { v.w[0] = a0; v.w[1] = v.w[2] = uint64_t(int64_t(a0) >> 63); return v; }
-  const uint64_t a1 = p[stride];
-  if (order == 2) {
-    const uint64_t ext = uint64_t(int64_t(a1) >> 63);
-    v.w[0] = a0 | (a1 << 63); v.w[1] = (a1 >> 1) | (ext << 63); v.w[2] = ext; return v;
-  }
-  const uint64_t a2 = p[2 * stride], ext = uint64_t(int64_t(a2) >> 63);
-  v.w[0] = a0 | (a1 << 63); v.w[1] = (a1 >> 1) | (a2 << 62); v.w[2] = (a2 >> 2) | (ext << 62);
-  return v;
-}
-__device__ __forceinline__ void store_limbs(U192 v, uint64_t* p, int64_t stride, int order) {
-  constexpr uint64_t m63 = 0x7fffffffffffffffull;
-  if (order == 1) { p[0] = v.w[0]; return; }
-  p[0] = v.w[0] & m63; sar63(v);
-  if (order == 2) { p[stride] = v.w[0]; return; }
-  p[stride] = v.w[0] & m63; sar63(v);
-  p[2 * stride] = v.w[0];
-}
 
 // KMAX: compile-time bound on the number of moduli (keeps the residues in registers).
 template <int KMAX, int COLS>

@@ -50,6 +50,18 @@ void hyacinB200GramResidues(const hyacinHandle_t* handle, int32_t N, int32_t mod
 void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, int32_t moduli, const uint8_t* residues,
                            int32_t beta, int32_t orderC, uint64_t* Cpanel);
 
+/* Limb route, stage by stage.  hyacinB200QuantizeLimbs writes `order` planes of balanced base-256 digits of
+ * rint(a 2^vexp), laid out like the residue planes of hyacinB200QuantizeCrt (order = (u + 9) / 8 digits hold
+ * |q| <= 2^u).  hyacinB200GramLimbs adds sum_{i,j} 2^(8(i+j)) W_i^T W_j (rows ka0.. of the A operand, kb0.. of the
+ * B operand, kRows rows, order * kRows <= 131071) into one panel of the packed integer Gram (beta = 0 overwrites).
+ * Stage counterparts in the reference: src/quantize_limbs.cu:60-79; src/hyacin_herk.cpp:148-161 with
+ * src/limbs_diag.cu, src/limbs_cross_real.cu and src/limbs_cross_imag.cu. */
+void hyacinB200QuantizeLimbs(const hyacinHandle_t* handle, hyacinPrecision_t Atype, int32_t rows, int32_t N, const void* A,
+                             int32_t lda, const int32_t* vexp, int32_t order, int8_t* W, int64_t ldk);
+void hyacinB200GramLimbs(const hyacinHandle_t* handle, int32_t N, int32_t order, const int8_t* W, int64_t ldw,
+                         int64_t planeStride, int32_t ka0, int32_t kb0, int32_t kRows, int32_t beta, int32_t orderC,
+                         uint64_t* Cpanel);
+
 /* hyacinXherkBatch for callers that cannot allocate: same arguments, same exact integer Gram in C, but all
  * scratch (int8 residue planes, residue accumulators) lives in a fixed 64 MiB array that is part of the loaded
  * module instead of coming from handle->mempool.  It is meant for hosts that have handed the whole device to

@@ -244,3 +244,81 @@ def test_stage_outputs_equal_reference_library(hy, ref, atype, m, n, eps):
     assert torch.equal(out[0][2], out[1][2]), "packed integer Gram differs from the reference"
     assert out[0][3] == out[1][3]
     assert torch.equal(out[0][4], out[1][4]), "dequantised Gram bits differ from the reference"
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Limb route (balanced base-256 digits, digit-pair products on the tensor cores)
+# ---------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("atype,u", [(api.F64, 6), (api.F64, 40), (api.F64, 70), (api.F32_COMPLEX, 23)])
+def test_limb_quantizer_digits_recompose_the_quantised_value(hy, atype, u):
+    """sum_k digit_k 256^k equals rint(a 2^vexp) for every entry; digits are int8; padding rows are zero."""
+    torch = _torch()
+    rng = np.random.default_rng(800 + u)
+    m, n = 150, 11
+    A = random_matrix(rng, m, n, atype, zero_cols=(4,))
+    dA = to_device_colmajor(A, None, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    order = (u + 9) // 8
+    parts = 3 if atype & 1 else 1
+    ldk = 256
+    W = torch.full((order, n, parts * ldk), 77, dtype=torch.int8, device="cuda")
+    hy.quantize_limbs(atype, m, n, dA, m, vexp, order, W, ldk)
+    torch.cuda.synchronize()
+    Wh = W.cpu().numpy().astype(object)
+    q = O.quantize_ints(_oracle_input(A, atype), atype, vexp[0].cpu().numpy())
+    for p in range(parts):
+        src = q[0] if p == 0 else q[1] if p == 1 else [[-v for v in col] for col in q[0]]
+        got = sum(Wh[k, :, p * ldk:p * ldk + m] * (256 ** k) for k in range(order))
+        assert np.array_equal(got, np.array(src, dtype=object))
+        assert np.all(W.cpu().numpy()[:, :, p * ldk + m:(p + 1) * ldk] == 0)
+
+
+@pytest.mark.parametrize("atype,m,n,pad,seg_k,zero_cols", CASES)
+def test_forced_limb_route_gives_the_same_integer_gram(hy, atype, m, n, pad, seg_k, zero_cols):
+    """GramMatrixAlgorithm = 'L': packed integer Gram equals the oracle bit for bit, also when accumulating."""
+    torch = _torch()
+    rng = np.random.default_rng(1000 + m + n + atype)
+    A = random_matrix(rng, m, n, atype, zero_cols=zero_cols)
+    lda = m + pad
+    dA = to_device_colmajor(A, lda, atype)
+    u, cp, lp, tri = hy.herk_batch_init(_eps_for(atype), m, n, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, lda, atype, u, seg_k)
+    Ao = _oracle_input(A, atype)
+    want_vexp = O.column_exponents(Ao, atype, u, *segs)
+    want_C = O.gram_exact(Ao, atype, want_vexp[0], lp)
+    hy.h.GramMatrixAlgorithm = b"L"
+    try:
+        C = _run_herk(hy, dA, m, n, lda, atype, u, lp, cp, segs, vexp)
+        np.testing.assert_array_equal(C.cpu().numpy().view(np.uint64), want_C)
+        C2 = _run_herk(hy, dA, m, n, lda, atype, u, lp, cp, segs, vexp, beta=1, C=C)
+        np.testing.assert_array_equal(C2.cpu().numpy().view(np.uint64), O.gram_exact(Ao, atype, want_vexp[0], lp, C=want_C))
+    finally:
+        hy.h.GramMatrixAlgorithm = b"A"
+        hy.h.GramSegmentK = 8192
+
+
+@pytest.mark.parametrize("atype,m,n,eps,ref_alg", [(api.F64, 120000, 520, 1e-10, b"L"), (api.F64_COMPLEX, 40000, 300, 1e-12, b"L"),
+                                                     (api.F32, 9000, 260, 1e-5, b"L"), (api.F64, 150000, 520, 1e-10, b"C")])
+def test_limb_route_equals_reference_limb_route(hy, ref, atype, m, n, eps, ref_alg):
+    """Both libraries forced onto their limb decompositions (several K chunks on our side): identical integer
+    Gram, and identical to this build's CRT route.  Beyond 130816 rows the reference's limb route disagrees with
+    the reference's own CRT route (its K-chunked accumulation, src/hyacin_herk.cpp:117-137); there the checker is
+    the reference's CRT route."""
+    torch = _torch()
+    rng = np.random.default_rng(31337 + n)
+    A = random_matrix(rng, m, n, atype, col_scale_decades=1.0)
+    dA = to_device_colmajor(A, None, atype)
+    out = {}
+    for name, lib, alg in (("limbs", hy, b"L"), ("crt", hy, b"C"), ("ref", ref, ref_alg)):
+        lib.h.GramMatrixAlgorithm = alg
+        u, cp, lp, tri = lib.herk_batch_init(eps, m, n, atype)
+        segs, vexp = _run_exponents(lib, dA, m, n, m, atype, u)
+        C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
+        lib.herk_batch(segs[0], segs[1], segs[2], n, atype, dA, m, u, vexp, 0, lp, C)
+        torch.cuda.synchronize()
+        lib.h.GramMatrixAlgorithm = b"A"
+        out[name] = C
+    assert hy.status() == 0
+    assert torch.equal(out["limbs"], out["crt"])
+    assert torch.equal(out["limbs"], out["ref"])
