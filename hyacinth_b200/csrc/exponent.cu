@@ -11,6 +11,7 @@
 #include "hyb_internal.h"
 #include <cuda_fp16.h>
 #include <climits>
+#include <algorithm>
 
 namespace hyb {
 namespace {
@@ -112,6 +113,41 @@ column_exponent_kernel(const T* __restrict__ A, int64_t ld, int64_t seg_len, int
   }
 }
 
+// Transposed input ('T' / 'C'): the matrix is stored n x rows, so the n entries of one row of op(A) are
+// contiguous.  Threads map to consecutive real columns (complex columns count twice, which again gives
+// max(|re|, |im|)), each walks down kRowsPerCtaT rows of one segment keeping its own maximum, and folds it
+// into the table with atomicMin -- no cross-thread reduction at all.
+constexpr int kRowsPerCtaT = 2048;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+column_exponent_transposed_kernel(const T* __restrict__ A, int64_t ld, int mul, int64_t seg_rows, int64_t last_rows, int batches,
+                                  int blocks_per_segment, int n, int u, int32_t* __restrict__ vexp) {
+  using B = Bits<T>; using W = typename B::word;
+  const int jj = blockIdx.y * 256 + threadIdx.x;                 // real column index in [0, mul * n)
+  const int seg = blockIdx.x / blocks_per_segment, blk = blockIdx.x % blocks_per_segment;
+  if (jj >= mul * n) return;
+  const int64_t len = (seg + 1 == batches) ? last_rows : seg_rows;
+  int64_t r0 = int64_t(blk) * kRowsPerCtaT, r1 = r0 + kRowsPerCtaT; if (r1 > len) r1 = len;
+  if (r0 >= r1) return;
+  const T* p = A + jj + (int64_t(seg) * seg_rows + r0) * ld;
+  W best = 0;
+  int64_t i = r0;
+  for (; i + 4 <= r1; i += 4) {
+    const T a0 = p[0], a1 = p[ld], a2 = p[2 * ld], a3 = p[3 * ld];
+    p += 4 * ld;
+    W b0 = B::abs_bits(a0), b1 = B::abs_bits(a1), b2 = B::abs_bits(a2), b3 = B::abs_bits(a3);
+    b0 = b0 > b1 ? b0 : b1; b2 = b2 > b3 ? b2 : b3; b0 = b0 > b2 ? b0 : b2; best = b0 > best ? b0 : best;
+  }
+  for (; i < r1; ++i) { const W b = B::abs_bits(*p); p += ld; best = b > best ? b : best; }
+  const int e = B::frexp_exp(best);
+  if (e != INT_MAX) {
+    const int m = u - e, col = jj / mul;
+    atomicMin(&vexp[int64_t(1 + seg) * n + col], m);
+    atomicMin(&vexp[col], m);
+  }
+}
+
 __global__ void __launch_bounds__(256)
 vector_range_kernel(int n, int u, const int32_t* __restrict__ vexp, int32_t* __restrict__ seg_u) {
   __shared__ int32_t warp_best[8];
@@ -144,10 +180,21 @@ void run_exponents(cudaStream_t stream, int cplx, int batches, int seg_m, int la
                                                                      batches, blocks_per_segment, n, u, vexp);
 }
 
+template <typename T>
+void run_exponents_transposed(cudaStream_t stream, int cplx, int batches, int seg_m, int last_m, int n, const void* A, int64_t lda,
+                              int u, int32_t* vexp) {
+  const int mul = cplx ? 2 : 1;
+  const int64_t longest = batches > 1 ? std::max(seg_m, last_m) : last_m;
+  int blocks_per_segment = int((longest + kRowsPerCtaT - 1) / kRowsPerCtaT); if (blocks_per_segment < 1) blocks_per_segment = 1;
+  dim3 grid(unsigned(int64_t(batches) * blocks_per_segment), unsigned((int64_t(n) * mul + 255) / 256));
+  column_exponent_transposed_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(A), lda * mul, mul, seg_m, last_m, batches,
+                                                                 blocks_per_segment, n, u, vexp);
+}
+
 }  // namespace
 
 void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int batches, int seg_m, int last_m, int n,
-                             const void* A, int64_t lda, int u, int32_t* vexp) {
+                             const void* A, int64_t lda, int u, int32_t* vexp, char op) {
   const bool empty = batches <= 0 || u < 0;
   // Without rows or with a negative bit budget only the global row is defined (all columns "zero").
   int64_t count = empty ? int64_t(n) : int64_t(batches + 1) * n;
@@ -156,6 +203,16 @@ void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int b
   if (empty) return;
   count_launch();
   const int cplx = is_complex(atype);
+  if (op == 'T' || op == 'C') {
+    switch (base_type(atype)) {
+      case HYACIN_F64: run_exponents_transposed<double>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;
+      case HYACIN_F32: run_exponents_transposed<float>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;
+      case HYACIN_F16: run_exponents_transposed<__half>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;
+      default: break;
+    }
+    HYB_CUDA(cudaGetLastError());
+    return;
+  }
   switch (base_type(atype)) {
     case HYACIN_F64: run_exponents<double>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;
     case HYACIN_F32: run_exponents<float>(stream, cplx, batches, seg_m, last_m, n, A, lda, u, vexp); break;

@@ -118,16 +118,20 @@ bool build_gram(const hyacinHandle_t* h, double eps, char op, int M, int N, hyac
   hyacinXherkBatchInit(h, eps, uint64_t(globalM), N, type, &u, &cp, &lp, &tri);
   int32_t* vexp = pool_alloc<int32_t>(h, size_t(batches + 1) * N);
   uint64_t* C = pool_alloc<uint64_t>(h, size_t(cp) * lp * tri);
-  const void* An = A; int ldn = lda; void* AH = nullptr;
   if (op == 'T' || op == 'C') {
-    AH = pool_alloc<char>(h, size_t(M) * N * elem_bytes(type));
-    convert_copy(h->cudaStream, op, M, N, type, A, lda, type, AH, M);
-    An = AH; ldn = M;
+    // The reference first writes a transposed copy of the whole input (src/lra.cpp:63-65); here the exponent
+    // pass and the quantisers read the stored layout directly (transposing 64 x 32 tiles through shared
+    // memory), which saves M x N elements of workspace and two passes over them.  Same integers either way.
+    timer_mark(h, Segment::Distributed);
+    launch_column_exponents(h->cudaStream, type, batches, seg, lastM, N, A, lda, u, vexp, op);
+    hyacinAllReduceVExp(h, uint64_t(N), vexp);
+    timer_mark(h, Segment::Distributed);
+    if (lp > 0) herk_any(h, M, N, type, A, lda, op, u, vexp, 0, lp, C);
+  } else {
+    hyacinXquantizeScaleBatch(h, batches, seg, lastM, N, type, A, lda, u, vexp);
+    hyacinAllReduceVExp(h, uint64_t(N), vexp);
+    hyacinXherkBatch(h, batches, seg, lastM, N, type, A, lda, u, vexp, 0, lp, C);
   }
-  hyacinXquantizeScaleBatch(h, batches, seg, lastM, N, type, An, ldn, u, vexp);
-  hyacinAllReduceVExp(h, uint64_t(N), vexp);
-  hyacinXherkBatch(h, batches, seg, lastM, N, type, An, ldn, u, vexp, 0, lp, C);
-  pool_free(h, AH);
   hyacinAllReduce1Drow(h, cp, lp, tri, C);
   hyacinPrecision_t gtype = HYACIN_F64;
   hyacinXdequantizeInit(h, N, lp, C, vexp, type, &gtype, &gbytes);

@@ -62,7 +62,7 @@ void status_check(const hyacinHandle_t* handle, const char* where) {
                               "the integer Gram of that call is invalid\n", v, where);
 }
 
-static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda,
+static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
                      int u, const int32_t* vexp, int beta, int order, uint64_t* C) {
   cudaStream_t stream = handle->cudaStream;
   const int cplx = is_complex(atype), parts = cplx ? 3 : 1;
@@ -85,8 +85,8 @@ static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPr
     for (int64_t c0 = 0; c0 < g; c0 += plan.chunk_rows) {
       const int rc = int(std::min<int64_t>(plan.chunk_rows, g - c0));
       const int64_t ldk = (rc + kStageK - 1) / kStageK * kStageK;
-      const char* src = static_cast<const char*>(A) + size_t(row + c0) * elem;
-      launch_quantize_crt(stream, atype, rc, n, src, lda, vexp, plan, W, ldk);
+      const char* src = static_cast<const char*>(A) + size_t(row + c0) * elem * (op == 'N' ? 1 : size_t(lda));
+      launch_quantize_crt(stream, atype, rc, n, src, lda, vexp, plan, W, ldk, op);
       GramLaunch gl{};
       gl.w = W; gl.ldw = ldk * parts; gl.plane_stride = gl.ldw * n;
       gl.ka0 = 0; gl.kb0 = 0; gl.k_rows = int(ldk) * (cplx ? 2 : 1); gl.n = n; gl.moduli = plan.moduli;
@@ -109,7 +109,7 @@ static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPr
 // multiplied on the tensor cores; pairs with the same shift share a TMEM accumulator and the epilogue adds it
 // into the packed integer Gram at bit 8 (i + j).  order^2 tile products per row chunk against `moduli` for the
 // CRT route, so it is the cheaper one only for small bit budgets (and whenever the caller forces it).
-static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda,
+static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
                        int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
   cudaStream_t stream = handle->cudaStream;
   const int cplx = is_complex(atype), parts = cplx ? 3 : 1, kmul = cplx ? 2 : 1;
@@ -127,8 +127,8 @@ static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacin
   for (int64_t c0 = 0; c0 < rows; c0 += chunk) {
     const int rc = int(std::min<int64_t>(chunk, rows - c0));
     const int64_t ldk = (rc + kStageK - 1) / kStageK * kStageK;
-    const char* src = static_cast<const char*>(A) + size_t(c0) * elem;
-    launch_quantize_limbs(stream, atype, rc, n, src, lda, vexp, order, W, ldk);
+    const char* src = static_cast<const char*>(A) + size_t(c0) * elem * (op == 'N' ? 1 : size_t(lda));
+    launch_quantize_limbs(stream, atype, rc, n, src, lda, vexp, order, W, ldk, op);
     GramLimbLaunch gl{};
     gl.w = W; gl.ldw = ldk * parts; gl.plane_stride = gl.ldw * n; gl.ka0 = 0; gl.kb0 = 0; gl.k_rows = int(ldk) * kmul;
     gl.n = n; gl.order = order; gl.limb_panels = order_c; gl.overwrite = (first && beta == 0) ? 1 : 0;
@@ -143,7 +143,25 @@ static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacin
 }
 
 // 'L' forces limbs, 'C' forces CRT; otherwise the route with fewer tile products per row chunk is taken.
-bool use_limb_route(char algorithm, int u, int cplx, int64_t rows) {
+static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows);
+
+// Integer Gram of op(A) (rows x n): the body of hyacinXherkBatch, with the transposed layouts the fits pass in.
+void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
+              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
+  const int cplx = is_complex(atype);
+  if (rows <= 0 || u < 0) {
+    // Nothing to add: an overwrite still has to define C (src/hyacin_herk.cpp:287).
+    if (beta == 0) {
+      const uint64_t tri = (uint64_t(n) * n + n) / 2;
+      HYB_CUDA(cudaMemsetAsync(C, 0, tri * uint64_t(order_c) * (1 + cplx) * sizeof(uint64_t), handle->cudaStream));
+    }
+    return;
+  }
+  if (use_limb_route(handle->GramMatrixAlgorithm, u, cplx, rows)) herk_limbs(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
+  else herk_crt(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
+}
+
+static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows) {
   if (algorithm == 'L' || algorithm == 'l') return true;
   if (algorithm == 'C' || algorithm == 'c') return false;
   const int order = (u + 9) / 8;
@@ -182,17 +200,7 @@ extern "C" void hyacinXherkBatch(const hyacinHandle_t* handle, int32_t batches, 
   if (int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX)) return;
   hyb::timer_mark(handle, hyb::Segment::Distributed);
   const int64_t rows = batches <= 1 ? int64_t(lastM) : int64_t(batches - 1) * segM + lastM;
-  const int cplx = hyb::is_complex(Atype);
-  if (rows <= 0 || u < 0) {
-    // Nothing to add: an overwrite still has to define C (src/hyacin_herk.cpp:287).
-    if (beta == 0) {
-      const uint64_t tri = (uint64_t(N) * N + N) / 2;
-      HYB_CUDA(cudaMemsetAsync(C, 0, tri * uint64_t(orderC) * (1 + cplx) * sizeof(uint64_t), handle->cudaStream));
-    }
-    return;
-  }
-  if (hyb::use_limb_route(handle->GramMatrixAlgorithm, u, cplx, rows)) hyb::herk_limbs(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
-  else hyb::herk_crt(handle, rows, N, Atype, A, lda, u, vexp, beta ? 1 : 0, orderC, C);
+  hyb::herk_any(handle, rows, N, Atype, A, lda, 'N', u, vexp, beta, orderC, C);
 }
 
 extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,

@@ -67,6 +67,10 @@ __host__ __device__ inline void tile_coords(int n_tiles_y, int t, int* ty, int* 
   }
 }
 
+// Integer Gram of op(A): what hyacinXherkBatch does, for any of the three input layouts.
+void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
+              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C);
+
 // Plan of one hyacinXherkBatch call: how many moduli, how rows are grouped and chunked.
 struct CrtPlan {
   int moduli;          // number of CRT moduli (prefix of crt::kModulus)
@@ -82,17 +86,18 @@ CrtPlan make_crt_plan(int u, int cplx, int64_t rows);
 // ---------------------------------------------------------------------------------------------------
 
 // Column exponents: fills vexp[(batches+1) x N].  Reference behaviour: src/fp_exponent.cu:45-51.
+// op 'N': A is rows x n column-major.  op 'T' / 'C': A is stored n x rows (the transposed input of a fit).
 void launch_column_exponents(cudaStream_t stream, hyacinPrecision_t atype, int batches, int seg_m, int last_m, int n,
-                             const void* A, int64_t lda, int u, int32_t* vexp);
+                             const void* A, int64_t lda, int u, int32_t* vexp, char op = 'N');
 // Bits needed per row segment (segU[batches]).  Reference behaviour: src/fp_exponent.cu:67-76.
 void launch_vector_range(cudaStream_t stream, int batches, int n, int u, const int32_t* vexp, int32_t* seg_u);
 
-// Quantise rows [0, rows) of A (column-major, 'N' orientation) into centred int8 residue planes
+// Quantise rows [0, rows) of op(A) into centred int8 residue planes (op as for launch_column_exponents)
 //   W[modulus][column][part * ldk + row]     (ldk a multiple of kStageK; rows in [rows, ldk) are zeroed)
 // Real input has one part.  Complex input has three, stacked along K inside each column: real, imaginary,
 // negated real -- so that rows [0, 2 ldk) are the operand (re; im) and rows [ldk, 3 ldk) the operand (im; -re).
 void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
-                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk);
+                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk, char op = 'N');
 
 // Residue Gram of one chunk.  For every modulus m and every upper-triangle tile:
 //   R[m][tile][y][x] = (accumulate ? R : 0) + sum_{k < k_rows} W[m][y][ka0 + k] * W[m][x][kb0 + k]  (mod m), a byte.
@@ -123,7 +128,7 @@ void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g);
 // Quantise rows of A into `order` planes of balanced base-256 digits (same plane layout as launch_quantize_crt).
 // Reference counterpart: src/quantize_limbs.cu:29-79.
 void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
-                           const int32_t* vexp, int order, int8_t* W, int64_t ldk);
+                           const int32_t* vexp, int order, int8_t* W, int64_t ldk, char op = 'N');
 
 // CRT reconstruction of `moduli` residue planes into the packed 63-bit-limb Gram:
 //   C[panel][order][tri] = (beta ? C : 0) + value.  Reference counterpart: src/crt_reconstruct_real.cu:51-92.

@@ -30,6 +30,7 @@ struct QuantParams {
   const int32_t* vexp;
   int8_t* W; int64_t col_pitch, plane_pitch, part_pitch;   // bytes; part_pitch = rows per part (ldk)
   int rows, ldk, n, moduli, value_bytes;
+  int op;                                   // 0: A is rows x n ('N'); 1: A is stored n x rows ('T'); 2: same, conjugated ('C')
   QuantConsts k;                            // kernel parameters live in the constant bank
 };
 
@@ -91,21 +92,68 @@ __device__ __forceinline__ void load_rows(const T* __restrict__ src, int valid, 
     for (int c = 0; c < kReal; ++c) v[r][c] = (load_as_double<T>(&raw[r * kReal + c]) * s1) * s2;
 }
 
-template <typename T, int NW, int PARTS>
-__global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
-  const int col = blockIdx.y;
-  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kRows;
-  if (row0 >= p.ldk) return;
-  const int expon = p.vexp[col];
-  // a * 2^expon as two exact scalings: the halves stay representable for every admissible exponent, and a
-  // product that leaves the normal range on the way is far below 1/2 at the end, i.e. rounds to zero anyway.
-  double s1 = 0.0, s2 = 0.0;
-  if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+// Front end shared by both quantisers: which (column, first row) this thread converts and the kRows scaled
+// values a * 2^vexp[col] of that column.
+//   TRANS = false ('N'): grid.x covers ldk / (kRows * 256) row groups, grid.y = columns; a thread reads eight
+//                        consecutive rows of its column straight from global memory (16-byte vectors).
+//   TRANS = true ('T' / 'C'): the matrix is stored transposed, so consecutive COLUMNS are contiguous.  A block
+//                        owns 64 rows x 32 columns, reads them with the column index on the fast lanes (256-byte
+//                        runs), transposes through shared memory, and then every thread again holds eight
+//                        consecutive rows of one column.  This replaces the transposed copy of the whole matrix
+//                        that the reference makes before quantising (src/lra.cpp:63-65, src/matcopy.cu:36-43).
+template <typename T, int PARTS, bool TRANS>
+__device__ __forceinline__ bool fetch_scaled(const void* A, int64_t lda, const int32_t* __restrict__ vexp, int rows, int ldk, int n, int op,
+                                             int& col, int& row0, double (&v)[kRows][PARTS == 1 ? 1 : 2]) {
   constexpr int kReal = PARTS == 1 ? 1 : 2;
-  const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0) * kReal;
-  int valid = p.rows - row0; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
-  double v[kRows][kReal];
-  load_rows<T, PARTS>(src, valid, s1, s2, v);
+  if constexpr (!TRANS) {
+    col = blockIdx.y;
+    row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kRows;
+    if (row0 >= ldk) return false;
+    const int expon = vexp[col];
+    // a * 2^expon as two exact scalings: the halves stay representable for every admissible exponent, and a
+    // product that leaves the normal range on the way is far below 1/2 at the end, i.e. rounds to zero anyway.
+    double s1 = 0.0, s2 = 0.0;
+    if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+    const T* src = static_cast<const T*>(A) + (int64_t(col) * lda + row0) * kReal;
+    int valid = rows - row0; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
+    load_rows<T, PARTS>(src, valid, s1, s2, v);
+    return true;
+  } else {
+    __shared__ double tile[kReal][64][33];
+    const int i0 = blockIdx.x * 64, j0 = blockIdx.y * 32;
+    const int tj = threadIdx.x & 31, ti = threadIdx.x >> 5;
+    const T* base = static_cast<const T*>(A);
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int i = i0 + ti + 8 * r, j = j0 + tj;
+      const bool in = i < rows && j < n;
+#pragma unroll
+      for (int c = 0; c < kReal; ++c) {
+        double x = in ? load_as_double<T>(base + (int64_t(j) + int64_t(i) * lda) * kReal + c) : 0.0;
+        if (c == 1 && op == 2) x = -x;
+        tile[c][ti + 8 * r][tj] = x;
+      }
+    }
+    __syncthreads();
+    const int cj = threadIdx.x >> 3, ci = threadIdx.x & 7;
+    col = j0 + cj; row0 = i0 + ci * kRows;
+    if (col >= n || row0 >= ldk) return false;
+    const int expon = vexp[col];
+    double s1 = 0.0, s2 = 0.0;
+    if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+      for (int c = 0; c < kReal; ++c) v[r][c] = (tile[c][ci * kRows + r][cj] * s1) * s2;
+    return true;
+  }
+}
+
+template <typename T, int NW, int PARTS, bool TRANS>
+__global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
+  constexpr int kReal = PARTS == 1 ? 1 : 2;
+  int col, row0; double v[kRows][kReal];
+  if (!fetch_scaled<T, PARTS, TRANS>(p.A, p.lda, p.vexp, p.rows, p.ldk, p.n, p.op, col, row0, v)) return;
 
   int8_t* dst = p.W + int64_t(col) * p.col_pitch + row0;
 #pragma unroll
@@ -141,22 +189,14 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
 struct LimbParams {
   const void* A; int64_t lda; const int32_t* vexp;
   int8_t* W; int64_t col_pitch, plane_pitch, part_pitch;
-  int rows, ldk, n, order;
+  int rows, ldk, n, order, op;
 };
 
-template <typename T, int NW, int PARTS>
+template <typename T, int NW, int PARTS, bool TRANS>
 __global__ void __launch_bounds__(256) quantize_limbs_kernel(const __grid_constant__ LimbParams p) {
-  const int col = blockIdx.y;
-  const int row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kRows;
-  if (row0 >= p.ldk) return;
-  const int expon = p.vexp[col];
-  double s1 = 0.0, s2 = 0.0;
-  if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
   constexpr int kReal = PARTS == 1 ? 1 : 2;
-  const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0) * kReal;
-  int valid = p.rows - row0; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
-  double v[kRows][kReal];
-  load_rows<T, PARTS>(src, valid, s1, s2, v);
+  int col, row0; double v[kRows][kReal];
+  if (!fetch_scaled<T, PARTS, TRANS>(p.A, p.lda, p.vexp, p.rows, p.ldk, p.n, p.op, col, row0, v)) return;
   // bias words: 0x80 in each of the `order` low bytes
   uint32_t bias[3];
 #pragma unroll
@@ -199,26 +239,40 @@ __global__ void __launch_bounds__(256) quantize_limbs_kernel(const __grid_consta
 
 template <typename T, int PARTS>
 void launch_limbs_typed(cudaStream_t stream, const LimbParams& p) {
-  dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
   const int nw = (p.order + 3) / 4;
-  if (nw <= 1) quantize_limbs_kernel<T, 1, PARTS><<<grid, 256, 0, stream>>>(p);
-  else if (nw == 2) quantize_limbs_kernel<T, 2, PARTS><<<grid, 256, 0, stream>>>(p);
-  else quantize_limbs_kernel<T, 3, PARTS><<<grid, 256, 0, stream>>>(p);
+  if (p.op == 0) {
+    dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
+    if (nw <= 1) quantize_limbs_kernel<T, 1, PARTS, false><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_limbs_kernel<T, 2, PARTS, false><<<grid, 256, 0, stream>>>(p);
+    else quantize_limbs_kernel<T, 3, PARTS, false><<<grid, 256, 0, stream>>>(p);
+  } else {
+    dim3 grid(unsigned(p.ldk / 64), unsigned((p.n + 31) / 32));
+    if (nw <= 1) quantize_limbs_kernel<T, 1, PARTS, true><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_limbs_kernel<T, 2, PARTS, true><<<grid, 256, 0, stream>>>(p);
+    else quantize_limbs_kernel<T, 3, PARTS, true><<<grid, 256, 0, stream>>>(p);
+  }
 }
 
 template <typename T, int PARTS>
 void launch_typed(cudaStream_t stream, const QuantParams& p) {
-  dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
   const int nw = (p.value_bytes + 3) / 4;
-  if (nw <= 1) quantize_crt_kernel<T, 1, PARTS><<<grid, 256, 0, stream>>>(p);
-  else if (nw == 2) quantize_crt_kernel<T, 2, PARTS><<<grid, 256, 0, stream>>>(p);
-  else quantize_crt_kernel<T, 3, PARTS><<<grid, 256, 0, stream>>>(p);
+  if (p.op == 0) {
+    dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
+    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, false><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, false><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt_kernel<T, 3, PARTS, false><<<grid, 256, 0, stream>>>(p);
+  } else {
+    dim3 grid(unsigned(p.ldk / 64), unsigned((p.n + 31) / 32));
+    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, true><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, true><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt_kernel<T, 3, PARTS, true><<<grid, 256, 0, stream>>>(p);
+  }
 }
 
 }  // namespace
 
 void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
-                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk) {
+                         const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk, char op) {
   const int cplx = is_complex(atype);
   QuantParams p;
   for (int i = 0; i < crt::kMaxModuli; ++i) {   // the bias depends on the byte width of the values
@@ -229,6 +283,7 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
   p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;
   p.part_pitch = ldk; p.col_pitch = ldk * (cplx ? 3 : 1); p.plane_pitch = p.col_pitch * n;
   p.rows = rows; p.ldk = int(ldk); p.n = n; p.moduli = plan.moduli; p.value_bytes = plan.value_bytes;
+  p.op = op == 'T' ? 1 : op == 'C' ? 2 : 0;
   ProfileScope prof(stream, KernelKind::Quantize);
   count_launch();
   switch (int(atype)) {
@@ -244,13 +299,13 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
 }
 
 void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
-                           const int32_t* vexp, int order, int8_t* W, int64_t ldk) {
+                           const int32_t* vexp, int order, int8_t* W, int64_t ldk, char op) {
   if (order < 1 || order > crt::kMaxBytes) return;
   const int cplx = is_complex(atype);
   LimbParams p;
   p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;
   p.part_pitch = ldk; p.col_pitch = ldk * (cplx ? 3 : 1); p.plane_pitch = p.col_pitch * n;
-  p.rows = rows; p.ldk = int(ldk); p.n = n; p.order = order;
+  p.rows = rows; p.ldk = int(ldk); p.n = n; p.order = order; p.op = op == 'T' ? 1 : op == 'C' ? 2 : 0;
   ProfileScope prof(stream, KernelKind::Quantize);
   count_launch();
   switch (int(atype)) {

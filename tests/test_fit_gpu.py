@@ -211,3 +211,25 @@ def test_stage_functions_on_a_shared_gram(hy, ref):
     assert torch.equal(res[0][3], res[1][3])
     s1, s2 = res[0][1].cpu().numpy(), res[1][1].cpu().numpy()
     assert np.max(np.abs(s1 - s2)) <= 1e-12 * s2[0]
+
+
+@pytest.mark.parametrize("atype,op,m,n,eps", [(api.F64, "T", 2100, 150, 1e-9), (api.F64_COMPLEX, "C", 1300, 70, 1e-9),
+                                               (api.F32, "T", 5000, 300, 1e-4), (api.F16, "T", 700, 40, 1e-2),
+                                               (api.F32_COMPLEX, "T", 900, 50, 1e-4)])
+def test_transposed_input_gives_bitwise_the_same_fit_as_an_explicit_transpose(hy, atype, op, m, n, eps):
+    """op = 'T' / 'C' is quantised straight from the stored layout; the integer Gram, and with it every bit of S
+    and V, must equal what the fit produces from an explicitly transposed copy passed with op = 'N'."""
+    torch = _torch()
+    rng = np.random.default_rng(600 + m)
+    base = atype & ~1
+    A = _decaying_matrix(rng, m, n, (api.F64 | (atype & 1)), 8.0 if base == api.F64 else 3.0)      # op(A), m x n
+    if base == api.F32:
+        A = A.astype(np.complex64 if atype & 1 else np.float32)
+    stored = A.T if op == "T" else A.conj().T
+    d_op = to_device_colmajor(np.ascontiguousarray(stored), stored.shape[0] + 3, atype)
+    d_n = to_device_colmajor(np.ascontiguousarray(A), None, atype)
+    r1, S1, V1 = _tsvd(hy, d_op, op, m, n, n, stored.shape[0] + 3, eps, atype)
+    r2, S2, V2 = _tsvd(hy, d_n, "N", m, n, n, m, eps, atype)
+    assert r1 == r2 and r1 > 0
+    assert torch.equal(S1, S2) and torch.equal(V1, V2)
+    assert hy.status() == 0
