@@ -19,6 +19,7 @@
 #include "hyb_internal.h"
 #include "crt_tables.h"
 #include "limbs192.cuh"
+#include "ptx_sm100.cuh"
 #include <cuda.h>
 #include <mutex>
 
@@ -33,7 +34,6 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;           // 48 KiB
 constexpr int kThreads = 192;
 constexpr int kEpilogueWarps = 4;
 constexpr uint32_t kTmemCols = 512;                           // two accumulators of kTileX columns
-constexpr uint32_t kSpinLimit = 1u << 22;                     // bounded waits: a few seconds at most
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + 256 /*barriers*/;
 
 struct ModConsts {
@@ -53,40 +53,7 @@ struct GramParams {
   ModConsts k;
 };
 
-// ---- PTX wrappers -----------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false if the wait expired or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) { if (*abort_flag) return false; __nanosleep(it > 4096 ? 256 : 32); }
-  }
-  *abort_flag = 1u;
-  *reinterpret_cast<volatile uint32_t*>(status) = code;      // plain store: the word lives in mapped host memory
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(smem_dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
+using namespace ptx;
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
@@ -300,9 +267,7 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
 }
 
 // ---- host side ------------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+}  // namespace
 
 EncodeTiledFn encode_tiled() {
   static EncodeTiledFn fn = nullptr;
@@ -315,8 +280,6 @@ EncodeTiledFn encode_tiled() {
   });
   return fn;
 }
-
-}  // namespace
 
 TilePlan make_tile_plan(int n) {
   TilePlan t; t.n = n;
