@@ -284,15 +284,16 @@ extern "C" int32_t hyacinXGevd(const hyacinHandle_t* handle, double eps, int32_t
   eps = std::min(std::max(std::fabs(eps), machine_eps), 1.);
 
   const size_t gb = gram_elem_bytes(Gtype);
-  char* Rw = pool_alloc<char>(handle, size_t(N) * N * gb);
+  const int64_t ldr = factor_row_pitch(N, Gtype);
+  char* Rw = pool_alloc<char>(handle, size_t(N) * ldr * gb);
   int32_t* jpiv = pool_alloc<int32_t>(handle, N);
-  int rank = potrfp(handle, lrqr ? eps : 0., N, N, Gtype, G, ldg, Rw, jpiv);
+  int rank = potrfp(handle, lrqr ? eps : 0., N, N, Gtype, G, ldg, Rw, ldr, jpiv);
   pool_free(handle, jpiv);
   if (rank <= 0) { pool_free(handle, Rw); return 0; }
 
   const size_t lb = gram_elem_bytes(lt), rb = gram_elem_bytes(real_of(lt));
   char* A = pool_alloc<char>(handle, size_t(N) * rank * lb);
-  factor_to_columns(stream, N, rank, Gtype, Rw, lt, A, N);
+  factor_to_columns(stream, N, rank, Gtype, Rw, ldr, lt, A, N);
   pool_free(handle, Rw);
   char* sigma = pool_alloc<char>(handle, size_t(rank) * rb);
   char* U = pool_alloc<char>(handle, size_t(N) * rank * lb);
@@ -330,13 +331,14 @@ extern "C" int32_t hyacinXGinterp(const hyacinHandle_t* handle, double eps, int3
   const double machine_eps = base_type(lt) == HYACIN_F64 ? DBL_EPSILON : double(FLT_EPSILON);
   eps = std::min(std::max(std::fabs(eps), machine_eps), 1.);
   const size_t gb = gram_elem_bytes(Gtype);
-  char* Rw = pool_alloc<char>(handle, size_t(K) * N * gb);
-  const int rank = potrfp(handle, eps, K, N, Gtype, G, ldg, Rw, jpiv);
+  const int64_t ldr = factor_row_pitch(N, Gtype);
+  char* Rw = pool_alloc<char>(handle, size_t(K) * ldr * gb);
+  const int rank = potrfp(handle, eps, K, N, Gtype, G, ldg, Rw, ldr, jpiv);
   if (rank == N) interp_scatter(stream, N, N, jpiv, lt, nullptr, N, Atype, X, ldx);
   else if (rank > 0) {
     const size_t lb = gram_elem_bytes(lt);
     char* B = pool_alloc<char>(handle, size_t(rank) * N * lb);
-    factor_to_pivoted(stream, N, rank, Gtype, Rw, jpiv, lt, B, rank);
+    factor_to_pivoted(stream, N, rank, Gtype, Rw, ldr, jpiv, lt, B, rank);
     trsm_upper_left(handle, lt, rank, N - rank, B, rank);
     interp_scatter(stream, N, rank, jpiv, lt, B, rank, Atype, X, ldx);
     pool_free(handle, B);

@@ -11,7 +11,9 @@ size_t gram_elem_bytes(hyacinPrecision_t gtype);
 // column was chosen before step k).  jpiv: n one-based column indices, chosen columns first.  Stops at `cap`
 // rows or when the remaining trace is <= eps^2 * initial trace.  Blocks the host; returns the rank.
 int potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, hyacinPrecision_t gtype, const void* G, int64_t ldg,
-           void* Rw, int32_t* jpiv);
+           void* Rw, int64_t ldr, int32_t* jpiv);
+// Row pitch (in elements) to allocate Rw with: n rounded up so that a row is a whole number of 16-byte units.
+int64_t factor_row_pitch(int n, hyacinPrecision_t gtype);
 
 // dst (column-major, ldd) <- op(src) with element conversion.  op: 'N' copy, 'T' transpose, 'C' conjugate
 // transpose.  rows / cols describe dst.  Types are hyacinPrecision_t values 0..5 (F64, F32, F16, real/complex).
@@ -20,10 +22,10 @@ void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecis
 
 // A (n x rank, column-major, lda) <- R^H with rows in original order: A[i, k] = conj(Rw[k][i]) (0 beyond).
 // dst_type: F64 / F32 (real or complex, matching the Gram).
-void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, hyacinPrecision_t dst_type,
+void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, hyacinPrecision_t dst_type,
                        void* A, int64_t lda);
 // B (rank x n, column-major, ldb) <- R in PIVOTED column order: B[k, x] = Rw[k][jpiv[x] - 1], zero below the diagonal.
-void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, const int32_t* jpiv,
+void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, const int32_t* jpiv,
                        hyacinPrecision_t dst_type, void* B, int64_t ldb);
 // X (n x rank, ldx, type xtype) <- P [I; T^H]: row jpiv[x]-1 gets e_x for x < rank and conj(B[:, x]) otherwise.
 void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, hyacinPrecision_t b_type, const void* B, int64_t ldb,

@@ -73,11 +73,11 @@ void dispatch_dst(cudaStream_t stream, char op, int rows, int cols, int cplx, co
 // A[i + k lda] = conj(Rw[k][i]) -- the factor as an n x rank matrix in original row order.
 template <typename S, typename D, int CP>
 __global__ void __launch_bounds__(256)
-factor_to_columns_kernel(int n, int rank, const S* __restrict__ Rw, D* __restrict__ A, int64_t lda) {
+factor_to_columns_kernel(int n, int rank, const S* __restrict__ Rw, int64_t ldr, D* __restrict__ A, int64_t lda) {
   const int i = blockIdx.x * 256 + threadIdx.x, k = blockIdx.y;
   if (i >= n || k >= rank) return;
   for (int q = 0; q < CP; ++q) {
-    double v = Num<S>::load(Rw + (size_t(k) * n + i) * CP + q);
+    double v = Num<S>::load(Rw + (size_t(k) * ldr + i) * CP + q);
     Num<D>::store(A + (i + int64_t(k) * lda) * CP + q, q == 1 ? -v : v);
   }
 }
@@ -85,12 +85,12 @@ factor_to_columns_kernel(int n, int rank, const S* __restrict__ Rw, D* __restric
 // B[k + x ldb] = Rw[k][jpiv[x] - 1] for k <= x (upper trapezoid in pivoted column order), 0 below the diagonal.
 template <typename S, typename D, int CP>
 __global__ void __launch_bounds__(256)
-factor_to_pivoted_kernel(int n, int rank, const S* __restrict__ Rw, const int32_t* __restrict__ jpiv, D* __restrict__ B, int64_t ldb) {
+factor_to_pivoted_kernel(int n, int rank, const S* __restrict__ Rw, int64_t ldr, const int32_t* __restrict__ jpiv, D* __restrict__ B, int64_t ldb) {
   const int k = blockIdx.x * 256 + threadIdx.x, x = blockIdx.y;
   if (k >= rank || x >= n) return;
   const int i = jpiv[x] - 1;
   for (int q = 0; q < CP; ++q) {
-    double v = k <= x ? Num<S>::load(Rw + (size_t(k) * n + i) * CP + q) : 0.;
+    double v = k <= x ? Num<S>::load(Rw + (size_t(k) * ldr + i) * CP + q) : 0.;
     Num<D>::store(B + (k + int64_t(x) * ldb) * CP + q, v);
   }
 }
@@ -153,12 +153,12 @@ void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecis
   HYB_CUDA(cudaGetLastError());
 }
 
-void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, hyacinPrecision_t dst_type,
+void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, hyacinPrecision_t dst_type,
                        void* A, int64_t lda) {
   if (n <= 0 || rank <= 0) return;
   count_launch();
   dim3 grid((n + 255) / 256, rank);
-#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), static_cast<D*>(A), lda
+#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), ldr, static_cast<D*>(A), lda
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
   switch (base_type(gtype)) {
     case HYACIN_F32:
@@ -179,12 +179,12 @@ void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t g
   HYB_CUDA(cudaGetLastError());
 }
 
-void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, const int32_t* jpiv,
+void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, const int32_t* jpiv,
                        hyacinPrecision_t dst_type, void* B, int64_t ldb) {
   if (n <= 0 || rank <= 0) return;
   count_launch();
   dim3 grid((rank + 255) / 256, n);
-#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), jpiv, static_cast<D*>(B), ldb
+#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), ldr, jpiv, static_cast<D*>(B), ldb
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
   switch (base_type(gtype)) {
     case HYACIN_F32:

@@ -233,3 +233,68 @@ def test_transposed_input_gives_bitwise_the_same_fit_as_an_explicit_transpose(hy
     assert r1 == r2 and r1 > 0
     assert torch.equal(S1, S2) and torch.equal(V1, V2)
     assert hy.status() == 0
+
+
+def _synthetic_gram(rng, n, gtype, decades):
+    """Hermitian positive semi-definite n x n matrix in the storage format of a Gram type (column-major)."""
+    torch = _torch()
+    cplx = bool(gtype & 1)
+    B = rng.standard_normal((n, n)) + (1j * rng.standard_normal((n, n)) if cplx else 0)
+    Q = np.linalg.qr(B)[0]
+    s = 10.0 ** (-decades * np.arange(n) / max(n - 1, 1))
+    G = (Q * s ** 2) @ Q.conj().T
+    d = 10.0 ** rng.uniform(-1, 1, n)
+    G = G * np.outer(d, d)                                  # congruence keeps it Hermitian and semi-definite
+    G = 0.5 * (G + G.conj().T)
+    base = gtype & ~1
+    if base == api.F32:
+        arr = G.astype(np.complex64 if cplx else np.float32)
+        t = torch.from_numpy(np.ascontiguousarray(arr.T)).cuda()
+    elif base == api.F64:
+        arr = G.astype(np.complex128 if cplx else np.float64)
+        t = torch.from_numpy(np.ascontiguousarray(arr.T)).cuda()
+    else:                                                   # double-double: (hi, lo) pairs, lo = 0
+        arr = G.astype(np.complex128 if cplx else np.float64)
+        planes = [arr.real, arr.imag] if cplx else [arr]
+        dd = np.zeros((n, n, 2 * len(planes)))
+        for q, pl in enumerate(planes):
+            dd[:, :, 2 * q] = pl.T
+        t = torch.from_numpy(dd).cuda()
+    return t
+
+
+@pytest.mark.parametrize("gtype,n,cap", [
+    (api.F32, 130, 130),            # 520-byte rows: the factor's pitch is padded to 16 bytes
+    (api.F32, 512, 200),
+    (api.F64, 40, 40),
+    (api.F64, 1001, 600),           # odd n with 8-byte elements: padded pitch
+    (api.F64, 1500, 1500),
+    (api.F64_COMPLEX, 333, 333),
+    (api.DD, 1024, 700),
+    (api.DD_COMPLEX, 200, 200),
+    (api.DD_COMPLEX, 1024, 300),
+    (api.F32, 5000, 64),            # more column runs than SMs: blocks loop over runs
+])
+def test_pivoted_cholesky_pivots_identical_to_reference(hy, ref, gtype, n, cap):
+    """hyacinXGinterp on the same Gram matrix: rank, the whole one-based pivot array and the coefficients agree."""
+    torch = _torch()
+    rng = np.random.default_rng(1000 + n + gtype)
+    G = _synthetic_gram(rng, n, gtype, {api.F32: 2.0, api.F64: 6.0, api.DD: 12.0}[gtype & ~1])
+    xtype = (api.F32 if (gtype & ~1) == api.F32 else api.F64) | (gtype & 1)
+    xdt = {api.F32: torch.float32, api.F64: torch.float64}[xtype & ~1]
+    words = 2 if gtype & 1 else 1
+    eps = 1e-3 if (gtype & ~1) == api.F32 else 1e-9
+    out = []
+    for lib in (hy, ref):
+        Gc = G.clone()
+        jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+        X = torch.zeros((cap, n * words), dtype=xdt, device="cuda")        # N x cap, column-major
+        rank = lib.ginterp(eps, n, cap, xtype, X, n, jp, gtype, Gc, n)
+        torch.cuda.synchronize()
+        out.append((rank, jp.cpu().numpy(), X.cpu().numpy().astype(np.float64)))
+    assert out[0][0] == out[1][0] > 0
+    assert np.array_equal(out[0][1], out[1][1]), "pivots differ from the reference"
+    assert sorted(out[0][1].tolist()) == list(range(1, n + 1))
+    scale = max(1.0, np.abs(out[1][2]).max())
+    assert np.max(np.abs(out[0][2] - out[1][2])) <= (1e-2 if (gtype & ~1) == api.F32 else 1e-5) * scale   # triangular solves amplify rounding by the factor's condition
+    assert hy.status() == 0
