@@ -72,6 +72,7 @@ __device__ __forceinline__ void biased_words(double v, int value_bytes, bool neg
 // eight values, the loads are 16-byte vectors when the column is 16-byte aligned, and every plane receives one
 // 8-byte store per thread (256 contiguous bytes per warp).
 constexpr int kRows = 8;
+static_assert(crt::kModulus[0] == 256, "the quantiser takes the low byte as the residue of the first modulus");
 
 template <typename T, int PARTS>
 __device__ __forceinline__ void load_rows(const T* __restrict__ src, int valid, double s1, double s2, double (&v)[kRows][PARTS == 1 ? 1 : 2]) {
@@ -162,8 +163,11 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
 #pragma unroll
     for (int r = 0; r < kRows; ++r) biased_words<NW>(v[r][part == 1 ? 1 : 0], p.value_bytes, part == 2, w[r]);
     int8_t* out = dst + int64_t(part) * p.part_pitch;
-#pragma unroll 1
-    for (int i = 0; i < p.moduli; ++i) {
+    // Unrolled over the whole table with a uniform guard: the per-modulus constants then sit at fixed offsets of
+    // the parameter bank and feed the arithmetic instructions directly, with no loads and no loop bookkeeping.
+#pragma unroll
+    for (int i = 0; i < crt::kMaxModuli; ++i) {
+      if (i >= p.moduli) break;
       const uint32_t bias = p.k.bias[i], w0 = p.k.weight[i][0], w1 = p.k.weight[i][1], w2 = p.k.weight[i][2];
       const uint32_t magic = p.k.magic[i], modulus = p.k.modulus[i];
       uint32_t r8[kRows];
@@ -172,7 +176,8 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
         uint32_t t = __dp4a(w[r][0], w0, bias);
         if (NW > 1) t = __dp4a(w[r][1], w1, t);
         if (NW > 2) t = __dp4a(w[r][2], w2, t);
-        r8[r] = t - __umulhi(t, magic) * modulus;                       // exact: t * modulus < 2^32
+        // modulus 256 (first in the table): the low byte is the residue and the packing below takes only that byte
+        r8[r] = i == 0 ? t : t - __umulhi(t, magic) * modulus;          // exact: t * modulus < 2^32
       }
       // four residues per word by byte permutes (ALU pipe), then -128 per byte
       uint2 packed;
