@@ -103,7 +103,28 @@ bool stage_gemm(const hyacinHandle_t* h, hyacinPrecision_t t, char op, int m, in
     case HYACIN_F16: { __half one = __float2half(1.f), zero = __float2half(0.f); HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_R_16F, lda, B, CUDA_R_16F, ldb, &zero, C, CUDA_R_16F, ldc, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT)); return true; }
     case HYACIN_F64_COMPLEX: { cuDoubleComplex one = make_cuDoubleComplex(1., 0.), zero = make_cuDoubleComplex(0., 0.); HYB_LIB(cublasZgemm(b, opa, CUBLAS_OP_N, m, n, k, &one, (const cuDoubleComplex*)A, lda, (const cuDoubleComplex*)B, ldb, &zero, (cuDoubleComplex*)C, ldc)); return true; }
     case HYACIN_F32_COMPLEX: { cuComplex one = make_cuComplex(1.f, 0.f), zero = make_cuComplex(0.f, 0.f); HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_C_32F, lda, B, CUDA_C_32F, ldb, &zero, C, CUDA_C_32F, ldc, CUBLAS_COMPUTE_32F_EMULATED_16BFX9, CUBLAS_GEMM_DEFAULT)); return true; }
-    default: return false;   // complex half has no library GEMM; the caller falls back to the unsegmented fit
+    case HYACIN_F16_COMPLEX: {
+      // The library has no complex-half GEMM: split into planes and use two real GEMMs per block of rows,
+      //   [C_re | C_im] = A_re [B_re | B_im] + A_im [-B_im | B_re]
+      // (the arrangement of src/matmul_fp16_complex.cu; here with FP32 accumulation and any op(A) handled by
+      // the splitting kernel instead of one routine per transposition).
+      const int block = 8192;
+      __half* bp = pool_alloc<__half>(h, size_t(3) * k * n);
+      __half* ap = pool_alloc<__half>(h, size_t(2) * block * k);
+      __half* cp = pool_alloc<__half>(h, size_t(2) * block * n);
+      split_complex_half_b(h->cudaStream, k, n, B, ldb, bp, k);
+      const float one = 1.f, zero = 0.f;
+      for (int i = 0; i < m; i += block) {
+        const int rows = std::min(block, m - i);
+        split_complex_half(h->cudaStream, op, i, rows, k, A, lda, ap, ap + size_t(block) * k, rows);
+        HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, k, &one, ap, CUDA_R_16F, rows, bp + size_t(k) * n, CUDA_R_16F, k, &zero, cp, CUDA_R_16F, rows, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+        HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, k, &one, ap + size_t(block) * k, CUDA_R_16F, rows, bp, CUDA_R_16F, k, &one, cp, CUDA_R_16F, rows, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+        merge_complex_half(h->cudaStream, rows, n, cp, cp + size_t(rows) * n, rows, static_cast<char*>(C) + size_t(i) * 4, ldc);
+      }
+      pool_free(h, bp); pool_free(h, ap); pool_free(h, cp);
+      return true;
+    }
+    default: return false;
   }
 }
 
@@ -164,7 +185,7 @@ int interp_fit(const hyacinHandle_t* h, double eps, char op, int M, int N, int K
 int svd_fit_segmented(const hyacinHandle_t* h, double eps, char op, int M, int N, int K, hyacinPrecision_t type, const void* A, int lda, void* S, void* V, int ldv, int64_t globalM) {
   K = std::min(N, K); if (K <= 0) return 0;
   const int segments = N >= 512 ? int(std::floor(std::sqrt(double(N) / double(K)))) : 1;
-  if (segments <= 1 || int(type) == HYACIN_F16_COMPLEX) return svd_fit(h, eps, op, M, N, K, type, A, lda, S, V, ldv, globalM);
+  if (segments <= 1) return svd_fit(h, eps, op, M, N, K, type, A, lda, S, V, ldv, globalM);
   eps *= std::sqrt(0.5);
   const size_t eb = elem_bytes(type), rb = elem_bytes(real_of(type));
   const int quot = N / segments, rem = N % segments, n1 = quot + (rem ? 1 : 0);

@@ -31,6 +31,15 @@ void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t g
 void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, hyacinPrecision_t b_type, const void* B, int64_t ldb,
                     hyacinPrecision_t xtype, void* X, int64_t ldx);
 
+// Planar views of complex-half matrices for the segmented fit (the library has no complex-half GEMM).
+// split: re, im (rows x cols, column-major, ld) <- op(src) rows [row0, row0 + rows); op 'N': src is stored rows x cols,
+//        'T' / 'C': src is stored cols x rows (and conjugated for 'C').
+// split_b: three panels of cols columns each, (-im, re, im), so that [re | im] and [-im | re] are contiguous
+//        (rows x 2 cols) operands.  merge: dst complex <- (re, im).
+void split_complex_half(cudaStream_t stream, char op, int64_t row0, int rows, int cols, const void* src, int64_t lds, void* re, void* im, int64_t ld);
+void split_complex_half_b(cudaStream_t stream, int rows, int cols, const void* src, int64_t lds, void* panels, int64_t ld);
+void merge_complex_half(cudaStream_t stream, int rows, int cols, const void* re, const void* im, int64_t ld, void* dst, int64_t ldd);
+
 // Tail-energy rank rule on `n` singular values (descending); writes K values to `out`, the new rank to *rank.
 // suffix: scratch of max(n, 1) doubles.
 void find_rank(cudaStream_t stream, double eps_sq, int n, int K, hyacinPrecision_t sigma_type, const void* sigma, hyacinPrecision_t out_type,

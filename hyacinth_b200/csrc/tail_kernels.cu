@@ -137,6 +137,42 @@ __global__ void find_rank_kernel(double eps_sq, int n, int K, const R* __restric
   if (threadIdx.x == 0) *rank = s_count;
 }
 
+
+// ---- planar complex half ------------------------------------------------------------------------------------
+__global__ void split_complex_half_kernel(int trans, int conj, int64_t row0, int rows, int cols, const __half2* __restrict__ src, int64_t lds,
+                                          __half* __restrict__ re, __half* __restrict__ im, int64_t ld) {
+  // 32 x 32 tile through shared memory so that both the read and the write run along the fast index
+  __shared__ __half2 tile[32][33];
+  const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  if (!trans) {
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+      const int r = r0 + threadIdx.x, c = c0 + j;
+      if (r < rows && c < cols) { const __half2 v = src[row0 + r + int64_t(c) * lds]; re[r + int64_t(c) * ld] = v.x; im[r + int64_t(c) * ld] = v.y; }
+    }
+    return;
+  }
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + threadIdx.x, r = r0 + j;                   // stored cols x rows: element (c, row0 + r)
+    if (r < rows && c < cols) tile[j][threadIdx.x] = src[c + (row0 + r) * lds];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + threadIdx.x, c = c0 + j;
+    if (r < rows && c < cols) { const __half2 v = tile[threadIdx.x][j]; re[r + int64_t(c) * ld] = v.x; im[r + int64_t(c) * ld] = conj ? __hneg(v.y) : v.y; }
+  }
+}
+__global__ void split_complex_half_b_kernel(int rows, int cols, const __half2* __restrict__ src, int64_t lds, __half* __restrict__ panels, int64_t ld) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+  if (r >= rows) return;
+  const __half2 v = src[r + int64_t(c) * lds];
+  const int64_t panel = ld * cols, at = r + int64_t(c) * ld;
+  panels[at] = __hneg(v.y); panels[at + panel] = v.x; panels[at + 2 * panel] = v.y;
+}
+__global__ void merge_complex_half_kernel(int rows, int cols, const __half* __restrict__ re, const __half* __restrict__ im, int64_t ld,
+                                          __half2* __restrict__ dst, int64_t ldd) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+  if (r < rows) dst[r + int64_t(c) * ldd] = __halves2half2(re[r + int64_t(c) * ld], im[r + int64_t(c) * ld]);
+}
 }  // namespace
 
 void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecision_t src_type, const void* src, int64_t lds,
@@ -236,6 +272,24 @@ void find_rank(cudaStream_t stream, double eps_sq, int n, int K, hyacinPrecision
     default: break;
   }
 #undef RUN
+  HYB_CUDA(cudaGetLastError());
+}
+
+void split_complex_half(cudaStream_t stream, char op, int64_t row0, int rows, int cols, const void* src, int64_t lds, void* re, void* im, int64_t ld) {
+  if (rows <= 0 || cols <= 0) return;
+  const int trans = op == 'T' || op == 'C';
+  split_complex_half_kernel<<<dim3((rows + 31) / 32, (cols + 31) / 32), dim3(32, 8), 0, stream>>>(
+      trans, op == 'C', row0, rows, cols, static_cast<const __half2*>(src), lds, static_cast<__half*>(re), static_cast<__half*>(im), ld);
+  HYB_CUDA(cudaGetLastError());
+}
+void split_complex_half_b(cudaStream_t stream, int rows, int cols, const void* src, int64_t lds, void* panels, int64_t ld) {
+  if (rows <= 0 || cols <= 0) return;
+  split_complex_half_b_kernel<<<dim3((rows + 127) / 128, cols), 128, 0, stream>>>(rows, cols, static_cast<const __half2*>(src), lds, static_cast<__half*>(panels), ld);
+  HYB_CUDA(cudaGetLastError());
+}
+void merge_complex_half(cudaStream_t stream, int rows, int cols, const void* re, const void* im, int64_t ld, void* dst, int64_t ldd) {
+  if (rows <= 0 || cols <= 0) return;
+  merge_complex_half_kernel<<<dim3((rows + 127) / 128, cols), 128, 0, stream>>>(rows, cols, static_cast<const __half*>(re), static_cast<const __half*>(im), ld, static_cast<__half2*>(dst), ldd);
   HYB_CUDA(cudaGetLastError());
 }
 

@@ -298,3 +298,26 @@ def test_pivoted_cholesky_pivots_identical_to_reference(hy, ref, gtype, n, cap):
     scale = max(1.0, np.abs(out[1][2]).max())
     assert np.max(np.abs(out[0][2] - out[1][2])) <= (1e-2 if (gtype & ~1) == api.F32 else 1e-5) * scale   # triangular solves amplify rounding by the factor's condition
     assert hy.status() == 0
+
+
+@pytest.mark.parametrize("op", ["N", "C"])
+def test_segmented_fit_on_complex_half_input(hy, ref, op):
+    """hyacinTsvdFitSegmentN with complex-half storage: the stage products go through planar real GEMMs."""
+    rng = np.random.default_rng(77)
+    m, n, k, eps, atype = 3000, 1024, 128, 2e-2, api.F16_COMPLEX
+    r = 40
+    U = np.linalg.qr(rng.standard_normal((m, r)) + 1j * rng.standard_normal((m, r)))[0]
+    W = np.linalg.qr(rng.standard_normal((n, r)) + 1j * rng.standard_normal((n, r)))[0]
+    s = 30.0 * 10.0 ** (-3.0 * np.arange(r) / (r - 1))
+    A = (U * s) @ W.conj().T
+    stored = A if op == "N" else np.ascontiguousarray(A.conj().T)
+    dA = to_device_colmajor(stored, atype=atype)
+    lda = stored.shape[0]
+    r1, S1, V1 = _tsvd(hy, dA, op, m, n, k, lda, eps, atype, segment_n=True)
+    r2, S2, V2 = _tsvd(ref, dA, op, m, n, k, lda, eps, atype, segment_n=True)
+    assert r1 > 0 and abs(r1 - r2) <= 2                        # half-precision stage products: ranks may differ by a column
+    s1, s2 = S1.float().cpu().numpy(), S2.float().cpu().numpy()
+    q = min(r1, r2)
+    assert np.max(np.abs(s1[:q] - s2[:q])) <= 2e-2 * s2[0]
+    assert _rel_error(hy, dA, op, m, n, lda, r1, V1, atype) <= 3 * eps
+    assert hy.status() == 0
