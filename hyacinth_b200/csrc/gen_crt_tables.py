@@ -7,6 +7,10 @@ operand after centring (<= 256), the set must be pairwise coprime, and each pref
 a large product so that few moduli cover a given bit budget.  Large primes are taken as they are; each small
 prime enters through the largest number <= 256 whose smallest prime factor it is (2^8, 3*5*17, 7*31, 11*23,
 13*19), which spends the small primes without wasting a slot on a small modulus.
+
+A second set (namespace crt2m) serves complex input: every modulus there is odd and has a square root of -1
+(all its prime factors are 1 mod 4), so a complex value re + i im maps to the two residues re -+ iota im and the
+Hermitian Gram needs one integer product per entry pair instead of two.
 """
 import math
 from itertools import combinations
@@ -51,19 +55,39 @@ def choose_moduli():
     return mods
 
 
+def choose_moduli_2m():
+    """Odd numbers <= 256 whose prime factors are all 1 mod 4, pairwise coprime, largest first."""
+    def ok(n):
+        p, m = 2, n
+        while p * p <= m:
+            while m % p == 0:
+                if p % 4 != 1:
+                    return False
+                m //= p
+            p += 1
+        return m == 1 or m % 4 == 1
+    chosen = []
+    for n in range(255, 4, -2):
+        if ok(n) and all(math.gcd(n, c) == 1 for c in chosen):
+            chosen.append(n)
+    return chosen
+
+
+def sqrt_minus_one(m):
+    for i in range(2, m):
+        if (i * i + 1) % m == 0:
+            return i
+    raise ValueError(m)
+
+
 def words(v, n):
     return [(v >> (64 * i)) & (2**64 - 1) for i in range(n)]
 
 
-def main():
-    mods = choose_moduli()
-    out = []
-    emit = out.append
-    emit("// Generated by gen_crt_tables.py -- do not edit by hand.")
-    emit("#pragma once")
-    emit("#include <stdint.h>")
-    emit("namespace hyb { namespace crt {")
-    emit(f"constexpr int kMaxModuli = {NMOD};")
+def emit_set(emit, ns, prefix, mods, complex_set):
+    nmod = len(mods)
+    emit("namespace hyb { namespace " + ns + " {")
+    emit(f"constexpr int kMaxModuli = {nmod};")
     emit(f"constexpr int kMaxBytes = {NBYTES};")
     emit("// Pairwise-coprime moduli, each <= 256 so that centred residues fit an int8 operand.")
     emit("constexpr uint16_t kModulus[kMaxModuli] = { " + ", ".join(map(str, mods)) + " };")
@@ -79,23 +103,44 @@ def main():
     emit("constexpr uint32_t kMagicCeil[kMaxModuli] = { " + ", ".join(str(-(-2**32 // m) & 0xFFFFFFFF) + "u" for m in mods) + " };")
     emit("// floor(2^32 / m): quotient estimate (off by at most one) for any 32-bit t.")
     emit("constexpr uint32_t kMagicFloor[kMaxModuli] = { " + ", ".join(str(2**32 // m) + "u" for m in mods) + " };")
-    emit("// kByteWeight[i][w]: the four weights 256^(4w+b) mod m_i, b = 0..3, packed little-endian for dp4a.")
-    rows = []
-    for m in mods:
-        ws = []
-        for w in range(NBYTES // 4):
-            v = 0
-            for b in range(4):
-                v |= (pow(256, 4 * w + b, m) & 0xFF) << (8 * b)
-            ws.append(f"0x{v:08x}u")
-        rows.append("{ " + ", ".join(ws) + " }")
-    emit(f"constexpr uint32_t kByteWeight[kMaxModuli][{NBYTES // 4}] = {{\n  " + ",\n  ".join(rows) + " };")
+
+    def weight_table(name, comment, factor):
+        emit(comment)
+        rows = []
+        for m in mods:
+            f = factor(m)
+            ws = []
+            for w in range(NBYTES // 4):
+                v = 0
+                for b in range(4):
+                    v |= ((f * pow(256, 4 * w + b, m)) % m & 0xFF) << (8 * b)
+                ws.append(f"0x{v:08x}u")
+            rows.append("{ " + ", ".join(ws) + " }")
+        emit(f"constexpr uint32_t {name}[kMaxModuli][{NBYTES // 4}] = {{\n  " + ",\n  ".join(rows) + " };")
+
+    weight_table("kByteWeight", "// kByteWeight[i][w]: the four weights 256^(4w+b) mod m_i, b = 0..3, packed little-endian for dp4a.", lambda m: 1)
     emit("// kPow2Bias[i][nb-1] = (128 - 2^(8 nb - 1)) mod m_i: folded into the dp4a accumulator so that a value")
     emit("// biased by 2^(8 nb - 1) (to make its bytes unsigned) reduces to (q + 128) mod m_i.")
     rows = []
     for m in mods:
         rows.append("{ " + ", ".join(str((128 - 2 ** (8 * nb - 1)) % m) for nb in range(1, NBYTES + 1)) + " }")
     emit(f"constexpr uint16_t kPow2Bias[kMaxModuli][{NBYTES}] = {{\n  " + ",\n  ".join(rows) + " };")
+    if complex_set:
+        iota = {m: sqrt_minus_one(m) for m in mods}
+        emit("// iota_i with iota_i^2 = -1 mod m_i; a complex value maps to p = re - iota im and q = re + iota im.")
+        emit("constexpr uint16_t kImagUnit[kMaxModuli] = { " + ", ".join(str(iota[m]) for m in mods) + " };")
+        weight_table("kByteWeightMinusI", "// (-iota 256^(4w+b)) mod m_i: weights of the imaginary bytes in p.", lambda m: (m - iota[m]) % m)
+        weight_table("kByteWeightPlusI", "// (+iota 256^(4w+b)) mod m_i: weights of the imaginary bytes in q.", lambda m: iota[m])
+        emit("// Additive constants of p and q when re and im are both biased by B = 2^(8 nb - 1):")
+        emit("// kBiasP = (128 - B + iota B) mod m, kBiasQ = (128 - B - iota B) mod m.")
+        for name, sign in (("kBiasP", 1), ("kBiasQ", -1)):
+            rows = []
+            for m in mods:
+                rows.append("{ " + ", ".join(str((128 - 2 ** (8 * nb - 1) + sign * iota[m] * 2 ** (8 * nb - 1)) % m) for nb in range(1, NBYTES + 1)) + " }")
+            emit(f"constexpr uint16_t {name}[kMaxModuli][{NBYTES}] = {{\n  " + ",\n  ".join(rows) + " };")
+        emit("// With X = P^T Q (entry pair (y,x), (x,y)): Re = (X_yx + X_xy) / 2 and Im = (X_yx - X_xy) / (2 iota) mod m_i.")
+        emit("constexpr uint16_t kInvTwo[kMaxModuli] = { " + ", ".join(str(pow(2, -1, m)) for m in mods) + " };")
+        emit("constexpr uint16_t kInvTwoIota[kMaxModuli] = { " + ", ".join(str(pow(2 * iota[m], -1, m)) for m in mods) + " };")
     emit("// Garner: kInv[j][i] = m_j^-1 mod m_i for j < i (0 elsewhere).")
     rows = []
     for j, mj in enumerate(mods):
@@ -111,16 +156,32 @@ def main():
         half_rows.append("{ " + ", ".join(f"0x{w:016x}ull" for w in words(P // 2, 3)) + " }")
     emit("constexpr uint64_t kProduct[kMaxModuli][3] = {\n  " + ",\n  ".join(prod_rows) + " };")
     emit("constexpr uint64_t kHalfProduct[kMaxModuli][3] = {\n  " + ",\n  ".join(half_rows) + " };")
-    emit("} }  // namespace hyb::crt")
+    emit("} }  // namespace hyb::" + ns)
     emit("// Brace initialisers of the same tables for __constant__ device copies.")
-    emit("#define HYB_CRT_MODULUS_INIT { " + ", ".join(map(str, mods)) + " }")
-    emit("#define HYB_CRT_MAGIC_CEIL_INIT { " + ", ".join(str(-(-2**32 // m) & 0xFFFFFFFF) + "u" for m in mods) + " }")
+    emit(f"#define {prefix}_MODULUS_INIT {{ " + ", ".join(map(str, mods)) + " }")
+    emit(f"#define {prefix}_MAGIC_CEIL_INIT {{ " + ", ".join(str(-(-2**32 // m) & 0xFFFFFFFF) + "u" for m in mods) + " }")
     inv_rows = []
     for j, mj in enumerate(mods):
         inv_rows.append("{ " + ", ".join(str(pow(mj, -1, mi)) if j < i else "0" for i, mi in enumerate(mods)) + " }")
-    emit("#define HYB_CRT_INV_INIT { " + ", ".join(inv_rows) + " }")
-    emit("#define HYB_CRT_PRODUCT_INIT { " + ", ".join(prod_rows) + " }")
-    emit("#define HYB_CRT_HALF_PRODUCT_INIT { " + ", ".join(half_rows) + " }")
+    emit(f"#define {prefix}_INV_INIT {{ " + ", ".join(inv_rows) + " }")
+    emit(f"#define {prefix}_PRODUCT_INIT {{ " + ", ".join(prod_rows) + " }")
+    emit(f"#define {prefix}_HALF_PRODUCT_INIT {{ " + ", ".join(half_rows) + " }")
+    if complex_set:
+        emit(f"#define {prefix}_INV_TWO_INIT {{ " + ", ".join(str(pow(2, -1, m)) for m in mods) + " }")
+        emit(f"#define {prefix}_INV_TWO_IOTA_INIT {{ " + ", ".join(str(pow(2 * iota[m], -1, m)) for m in mods) + " }")
+
+
+def main():
+    out = []
+    emit = out.append
+    emit("// Generated by gen_crt_tables.py -- do not edit by hand.")
+    emit("#pragma once")
+    emit("#include <stdint.h>")
+    emit_set(emit, "crt", "HYB_CRT", choose_moduli(), False)
+    mods2 = choose_moduli_2m()
+    for a, b in combinations(mods2, 2):
+        assert math.gcd(a, b) == 1
+    emit_set(emit, "crt2m", "HYB_CRT2M", mods2, True)
     print("\n".join(out))
 
 

@@ -47,6 +47,7 @@ struct GramParams {
   int ka0, kb0;                 // first K row of the A / B operand inside a column
   int num_kblocks;              // k_rows / kStageK
   int num_tiles, tiles_y, moduli, accumulate;
+  int full;                     // 1: tile index = ty + tx tiles_y over all tiles (the product is not symmetric)
   // limb mode: planes are the balanced base-256 digits of the quantised values; the accumulator of shift s
   // collects every digit pair (i, j) with i + j = s and is added to the packed integer Gram at bit 8 s
   uint64_t* gram; int64_t tri; int n, order, limb_panels, overwrite;
@@ -78,6 +79,10 @@ struct Barriers {
 // LIMBS = true : one work group per tile, 2 order - 1 accumulators (one per shift) handled one after the other by
 //                the same CTA, epilogue = read-modify-write of the packed 63-bit limbs (the same thread owns an
 //                entry for every shift, so no atomics are needed).
+__device__ __forceinline__ void tile_of(const GramParams& p, int t, int* ty, int* tx) {
+  if (p.full) { *tx = t / p.tiles_y; *ty = t - *tx * p.tiles_y; } else tile_coords(p.tiles_y, t, ty, tx);
+}
+
 template <bool LIMBS>
 __global__ void __launch_bounds__(kThreads, 1)
 gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p) {
@@ -108,7 +113,7 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
     if (lane == 0) {
       uint32_t stage = 0, phase = 0; bool ok = true;
       for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x) {
-        int ty, tx; tile_coords(p.tiles_y, LIMBS ? group : group % p.num_tiles, &ty, &tx);
+        int ty, tx; tile_of(p, LIMBS ? group : group % p.num_tiles, &ty, &tx);
         for (int sub = 0; sub < subs && ok; ++sub) {
           // plane pairs of this accumulator: (m, m) for residues; (i, sub - i) for limbs
           const int first = LIMBS ? (sub - (p.order - 1) > 0 ? sub - (p.order - 1) : 0) : group / p.num_tiles;
@@ -171,7 +176,7 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
       if constexpr (LIMBS) {
-        int ty, tx; tile_coords(p.tiles_y, tile, &ty, &tx);
+        int ty, tx; tile_of(p, tile, &ty, &tx);
         const int y = ty * kTileY + row;
         const bool store_only = p.overwrite && sub == 0;        // first shift of the first chunk of a beta = 0 call
 #pragma unroll 1
@@ -282,14 +287,16 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
   GramParams p{};
   p.residues = g.residues; p.status = g.status;
   p.ka0 = g.ka0; p.kb0 = g.kb0; p.num_kblocks = g.k_rows / kStageK;
-  p.num_tiles = tp.num_tiles; p.tiles_y = tp.tiles_y; p.moduli = g.moduli; p.accumulate = g.accumulate;
+  p.full = g.full ? 1 : 0;
+  p.num_tiles = p.full ? tp.tiles_y * tp.tiles_x : tp.num_tiles; p.tiles_y = tp.tiles_y; p.moduli = g.moduli; p.accumulate = g.accumulate;
   for (int i = 0; i < crt::kMaxModuli; ++i) {
-    const uint32_t m = crt::kModulus[i];
-    p.k.modulus[i] = m; p.k.magic[i] = crt::kMagicFloor[i];
+    const bool have = g.table == 0 || i < crt2m::kMaxModuli;
+    const uint32_t m = !have ? 1u : g.table == 0 ? crt::kModulus[i] : crt2m::kModulus[i];
+    p.k.modulus[i] = m; p.k.magic[i] = !have ? 0u : g.table == 0 ? crt::kMagicFloor[i] : crt2m::kMagicFloor[i];
     p.k.bias[i] = (0x80000000u / m) * m;
   }
   HYB_CUDA(cudaFuncSetAttribute(gram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-  const int items = g.moduli * tp.num_tiles;
+  const int items = g.moduli * p.num_tiles;
   int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > items) grid = items;
   if (grid <= 0 || p.num_kblocks <= 0) return;
   ProfileScope prof(stream, KernelKind::Gram);

@@ -19,10 +19,19 @@ namespace hyb {
 
 static int ceil_log2_u64(uint64_t v) { int l = 0; while (l < 64 && (uint64_t(1) << l) < v) ++l; return l; }
 
-CrtPlan make_crt_plan(int u, int cplx, int64_t rows) {
+CrtPlan make_crt_plan(int u, int cplx, int64_t rows, bool allow_two_m) {
   CrtPlan p{}; if (u < 0 || rows <= 0) return p;
   p.value_bytes = (u + 9) / 8;                       // |q| <= 2^u must stay below the bias 2^(8 nb - 1)
   auto bits_for = [&](int64_t g) { return 2 * u + 1 + cplx + ceil_log2_u64(uint64_t(g)); };
+  if (cplx && allow_two_m && bits_for(rows) <= crt2m::kRangeBits[crt2m::kMaxModuli - 1]) {
+    // complex input whose whole call fits the moduli with a square root of -1: half the tensor work
+    const int need = bits_for(rows);
+    int k = 1; while (k < crt2m::kMaxModuli && crt2m::kRangeBits[k - 1] < need) ++k;
+    p.moduli = k; p.group_rows = int(std::min<int64_t>(rows, int64_t(1) << 30)); p.two_m = 1;
+    p.chunk_rows = int(std::min<int64_t>(65536, (rows + kStageK - 1) / kStageK * kStageK));
+    if (rows <= (int64_t(1) << 30)) return p;
+    p = CrtPlan{}; p.value_bytes = (u + 9) / 8;
+  }
   int64_t group = rows;
   const int max_bits = crt::kRangeBits[crt::kMaxModuli - 1];
   if (bits_for(group) > max_bits) { group = 1; while (group * 2 <= rows && bits_for(group * 2) <= max_bits) group *= 2; }
@@ -71,6 +80,43 @@ static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPr
   if (plan.moduli == 0) return;
   const TilePlan tp = make_tile_plan(n);
   const size_t elem = (base_type(atype) == HYACIN_F64 ? 8 : base_type(atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);
+  if (plan.two_m) {
+    // X = P^T Q over all tiles, accumulated modulo m across the row chunks; then one pass turns X into the residues
+    // of the real and imaginary parts over the upper-triangle tiles, and each is reconstructed into its panel.
+    const size_t tile_bytes = size_t(kTileY) * kTileX;
+    const size_t full_bytes = size_t(plan.moduli) * tp.tiles_y * tp.tiles_x * tile_bytes, tri_bytes = size_t(plan.moduli) * tp.num_tiles * tile_bytes;
+    const size_t wb = size_t(plan.chunk_rows) * 2 * size_t(n) * plan.moduli;
+    int8_t* W = nullptr; uint8_t* X = nullptr; uint8_t* R = nullptr;
+    HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&W), wb, handle->mempool, stream));
+    HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&X), full_bytes, handle->mempool, stream));
+    HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&R), 2 * tri_bytes, handle->mempool, stream));
+    uint32_t* status = status_word_device(handle->DeviceID);
+    if (W && X && R && status) {
+      bool first = true;
+      for (int64_t c0 = 0; c0 < rows; c0 += plan.chunk_rows) {
+        const int rc = int(std::min<int64_t>(plan.chunk_rows, rows - c0));
+        const int64_t ldk = (rc + kStageK - 1) / kStageK * kStageK;
+        const char* src = static_cast<const char*>(A) + size_t(c0) * elem * (op == 'N' ? 1 : size_t(lda));
+        launch_quantize_crt(stream, atype, rc, n, src, lda, vexp, plan, W, ldk, op);
+        GramLaunch gl{};
+        gl.w = W; gl.ldw = ldk * 2; gl.plane_stride = gl.ldw * n;
+        gl.ka0 = 0; gl.kb0 = int(ldk); gl.k_rows = int(ldk); gl.n = n; gl.moduli = plan.moduli;
+        gl.accumulate = first ? 0 : 1; gl.sm_count = handle->DeviceSMs; gl.residues = X; gl.status = status;
+        gl.full = 1; gl.table = 1;
+        launch_gram_residues(stream, gl);
+        first = false;
+      }
+      launch_crt2m_rotate(stream, n, plan.moduli, X, R, R + tri_bytes);
+      launch_reconstruct(stream, n, plan.moduli, R, beta, order, C, 1);
+      launch_reconstruct(stream, n, plan.moduli, R + tri_bytes, beta, order, C + size_t(order) * tri, 1);
+    }
+    if (W) HYB_CUDA(cudaFreeAsync(W, stream));
+    if (X) HYB_CUDA(cudaFreeAsync(X, stream));
+    if (R) HYB_CUDA(cudaFreeAsync(R, stream));
+    if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "I8I32-GEMM-COMPLEX [algo=TN,crt-2m,tcgen05] [M=N=%d] [K=%lld] [Order=%d]\n",
+                                     n, (long long)rows, plan.moduli);
+    return;
+  }
   const size_t w_bytes = size_t(plan.chunk_rows) * parts * size_t(n) * plan.moduli;
   const size_t r_bytes = size_t(plan.moduli) * tp.num_tiles * size_t(kTileY) * kTileX;
   int8_t* W = nullptr; uint8_t* R = nullptr;
@@ -165,7 +211,7 @@ static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows) {
   if (algorithm == 'L' || algorithm == 'l') return true;
   if (algorithm == 'C' || algorithm == 'c') return false;
   const int order = (u + 9) / 8;
-  return order * order < make_crt_plan(u, cplx, rows).moduli;
+  return order * order < make_crt_plan(u, cplx, rows, false).moduli;
 }
 
 }  // namespace hyb
@@ -240,7 +286,7 @@ extern "C" uint32_t hyacinB200Status(int32_t clear) {
 
 extern "C" void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int32_t* moduli, int32_t* valueBytes,
                                   int32_t* groupRows, int32_t* chunkRows) {
-  const hyb::CrtPlan p = hyb::make_crt_plan(u, Complex ? 1 : 0, rows);
+  const hyb::CrtPlan p = hyb::make_crt_plan(u, Complex ? 1 : 0, rows, false);     // the stage hooks keep the three-part complex layout
   if (moduli) *moduli = p.moduli; if (valueBytes) *valueBytes = p.value_bytes;
   if (groupRows) *groupRows = p.group_rows; if (chunkRows) *chunkRows = p.chunk_rows;
 }

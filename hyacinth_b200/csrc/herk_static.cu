@@ -72,7 +72,7 @@ extern "C" int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32
     if (beta == 0) HYB_CUDA(cudaMemsetAsync(C, 0, size_t(tri) * orderC * (1 + cplx) * sizeof(uint64_t), stream));
     return 0;
   }
-  const CrtPlan plan = make_crt_plan(u, cplx, rows);
+  const CrtPlan plan = make_crt_plan(u, cplx, rows, false);
   if (plan.moduli == 0) return -1;
   const TilePlan tp = make_tile_plan(N);
   const size_t r_bytes = round_up(size_t(plan.moduli) * tp.num_tiles * size_t(kTileY) * kTileX, 256);

@@ -77,9 +77,11 @@ struct CrtPlan {
   int value_bytes;     // bytes needed for a biased quantised value (1..12)
   int group_rows;      // rows reconstructed together (residues accumulate across the chunks of a group)
   int chunk_rows;      // rows quantised and multiplied per kernel launch (multiple of kStageK)
+  int two_m;           // complex input through the moduli with a square root of -1 (crt2m tables, two planes p, q)
 };
 // u: quantisation bits of the call; cplx: 0/1; rows: rows of this call.  Returns moduli == 0 if impossible.
-CrtPlan make_crt_plan(int u, int cplx, int64_t rows);
+// allow_two_m: complex input may use the crt2m route when its moduli cover the whole call without grouping.
+CrtPlan make_crt_plan(int u, int cplx, int64_t rows, bool allow_two_m = true);
 
 // ---------------------------------------------------------------------------------------------------
 // Kernel launchers (all asynchronous on `stream`).
@@ -96,6 +98,8 @@ void launch_vector_range(cudaStream_t stream, int batches, int n, int u, const i
 //   W[modulus][column][part * ldk + row]     (ldk a multiple of kStageK; rows in [rows, ldk) are zeroed)
 // Real input has one part.  Complex input has three, stacked along K inside each column: real, imaginary,
 // negated real -- so that rows [0, 2 ldk) are the operand (re; im) and rows [ldk, 3 ldk) the operand (im; -re).
+// With plan.two_m complex input has two parts instead: p = re - iota im and q = re + iota im modulo each modulus of
+// the crt2m set (reference counterpart: src/quantize_crt_complex.cu:30-42).
 void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
                          const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk, char op = 'N');
 
@@ -109,8 +113,14 @@ struct GramLaunch {
   int ka0, kb0, k_rows, n, moduli, accumulate, sm_count;
   uint8_t* residues;            // [moduli][num_tiles][kTileY * kTileX]
   uint32_t* status;
+  int full;                     // 1: every tile (ty, tx) = index ty + tx tiles_y, for a product that is not symmetric
+  int table;                    // 0: moduli of crt, 1: moduli of crt2m
 };
 void launch_gram_residues(cudaStream_t stream, const GramLaunch& g);
+// crt2m: X = P^T Q over all tiles -> residues of the real and imaginary parts of the Hermitian Gram in the
+// upper-triangle tile layout: re = (X_yx + X_xy) / 2, im = (X_yx - X_xy) / (2 iota) modulo each modulus.
+// Reference counterpart: src/crt_rotate.cu.
+void launch_crt2m_rotate(cudaStream_t stream, int n, int moduli, const uint8_t* full_residues, uint8_t* re_residues, uint8_t* im_residues);
 
 // Limb Gram of one chunk, straight into the packed integer Gram (one panel: real or imaginary part):
 //   gram[y <= x] (+)= sum_{i, j < order} 2^(8 (i + j)) sum_{k < k_rows} W[i][y][ka0 + k] * W[j][x][kb0 + k]
@@ -132,8 +142,9 @@ void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int row
 
 // CRT reconstruction of `moduli` residue planes into the packed 63-bit-limb Gram:
 //   C[panel][order][tri] = (beta ? C : 0) + value.  Reference counterpart: src/crt_reconstruct_real.cu:51-92.
+// table: 0 = moduli of crt, 1 = moduli of crt2m.
 void launch_reconstruct(cudaStream_t stream, int n, int moduli, const uint8_t* residues, int beta, int order,
-                        uint64_t* C_panel);
+                        uint64_t* C_panel, int table = 0);
 
 // Largest bit length among the true-scale diagonal entries (written to *bits_out, device or pinned).
 void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, int32_t* bits_out);

@@ -188,6 +188,75 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
   }
 }
 
+// ---- complex input, moduli with a square root of -1 -------------------------------------------------------------
+// Every modulus m of the crt2m set has an iota with iota^2 = -1 (mod m), so the complex value re + i im is carried by
+// the two residues p = re - iota im and q = re + iota im, and P^T Q = Re(A^H A) + iota Im(A^H A) (mod m) entry by entry:
+// one integer product per pair of entries instead of the two that separate real and imaginary planes need
+// (reference: src/quantize_crt_complex.cu:30-42, with its own table).  iota is folded into the byte weights of
+// the imaginary part, so p and q are each four dp4a (for values of up to 8 bytes) and one reduction:
+//   p + 128 = bias_p + sum_b re_b (256^b mod m) + sum_b im_b (-iota 256^b mod m)        (sum < 2^22)
+// Planes: W[modulus][column][part * ldk + row], part 0 = p, part 1 = q.
+struct Quant2mConsts {
+  uint32_t modulus[crt2m::kMaxModuli], magic[crt2m::kMaxModuli], bias_p[crt2m::kMaxModuli], bias_q[crt2m::kMaxModuli];
+  uint32_t w_re[crt2m::kMaxModuli][3], w_im_p[crt2m::kMaxModuli][3], w_im_q[crt2m::kMaxModuli][3];
+};
+struct Quant2mParams {
+  const void* A; int64_t lda; const int32_t* vexp;
+  int8_t* W; int64_t col_pitch, plane_pitch, part_pitch;
+  int rows, ldk, n, moduli, value_bytes, op;
+  Quant2mConsts k;
+};
+
+template <typename T, int NW, bool TRANS>
+__global__ void __launch_bounds__(256) quantize_crt2m_kernel(const __grid_constant__ Quant2mParams p) {
+  int col, row0; double v[kRows][2];
+  if (!fetch_scaled<T, 3, TRANS>(p.A, p.lda, p.vexp, p.rows, p.ldk, p.n, p.op, col, row0, v)) return;
+  uint32_t wr[kRows][3], wi[kRows][3];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) { biased_words<NW>(v[r][0], p.value_bytes, false, wr[r]); biased_words<NW>(v[r][1], p.value_bytes, false, wi[r]); }
+  int8_t* out = p.W + int64_t(col) * p.col_pitch + row0;
+#pragma unroll
+  for (int i = 0; i < crt2m::kMaxModuli; ++i) {
+    if (i >= p.moduli) break;
+    const uint32_t magic = p.k.magic[i], modulus = p.k.modulus[i];
+    uint32_t rp[kRows], rq[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      uint32_t base = __dp4a(wr[r][0], p.k.w_re[i][0], 0u);
+      if (NW > 1) base = __dp4a(wr[r][1], p.k.w_re[i][1], base);
+      if (NW > 2) base = __dp4a(wr[r][2], p.k.w_re[i][2], base);
+      uint32_t tp = __dp4a(wi[r][0], p.k.w_im_p[i][0], base + p.k.bias_p[i]), tq = __dp4a(wi[r][0], p.k.w_im_q[i][0], base + p.k.bias_q[i]);
+      if (NW > 1) { tp = __dp4a(wi[r][1], p.k.w_im_p[i][1], tp); tq = __dp4a(wi[r][1], p.k.w_im_q[i][1], tq); }
+      if (NW > 2) { tp = __dp4a(wi[r][2], p.k.w_im_p[i][2], tp); tq = __dp4a(wi[r][2], p.k.w_im_q[i][2], tq); }
+      rp[r] = tp - __umulhi(tp, magic) * modulus;                       // exact: t < 2^23, t * modulus < 2^32
+      rq[r] = tq - __umulhi(tq, magic) * modulus;
+    }
+    uint2 pp, qq;
+    pp.x = __byte_perm(__byte_perm(rp[0], rp[1], 0x0040), __byte_perm(rp[2], rp[3], 0x0040), 0x5410) ^ 0x80808080u;
+    pp.y = __byte_perm(__byte_perm(rp[4], rp[5], 0x0040), __byte_perm(rp[6], rp[7], 0x0040), 0x5410) ^ 0x80808080u;
+    qq.x = __byte_perm(__byte_perm(rq[0], rq[1], 0x0040), __byte_perm(rq[2], rq[3], 0x0040), 0x5410) ^ 0x80808080u;
+    qq.y = __byte_perm(__byte_perm(rq[4], rq[5], 0x0040), __byte_perm(rq[6], rq[7], 0x0040), 0x5410) ^ 0x80808080u;
+    *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch) = pp;
+    *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch + p.part_pitch) = qq;
+  }
+}
+
+template <typename T>
+void launch_2m_typed(cudaStream_t stream, const Quant2mParams& p) {
+  const int nw = (p.value_bytes + 3) / 4;
+  if (p.op == 0) {
+    dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
+    if (nw <= 1) quantize_crt2m_kernel<T, 1, false><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt2m_kernel<T, 2, false><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt2m_kernel<T, 3, false><<<grid, 256, 0, stream>>>(p);
+  } else {
+    dim3 grid(unsigned(p.ldk / 64), unsigned((p.n + 31) / 32));
+    if (nw <= 1) quantize_crt2m_kernel<T, 1, true><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt2m_kernel<T, 2, true><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt2m_kernel<T, 3, true><<<grid, 256, 0, stream>>>(p);
+  }
+}
+
 // ---- balanced base-256 digits ("limbs") --------------------------------------------------------------------
 // q + sum_k 128 * 256^k has unsigned bytes b_k with q = sum_k (b_k - 128) 256^k, so digit k is simply byte k with
 // its top bit flipped: no carries.  `order` digits hold every |q| <= 2^(8 order - 2).
@@ -279,6 +348,28 @@ void launch_typed(cudaStream_t stream, const QuantParams& p) {
 void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
                          const int32_t* vexp, const CrtPlan& plan, int8_t* W, int64_t ldk, char op) {
   const int cplx = is_complex(atype);
+  if (plan.two_m) {
+    if (!cplx || plan.moduli > crt2m::kMaxModuli) return;
+    Quant2mParams q;
+    for (int i = 0; i < crt2m::kMaxModuli; ++i) {
+      q.k.modulus[i] = crt2m::kModulus[i]; q.k.magic[i] = crt2m::kMagicCeil[i];
+      q.k.bias_p[i] = crt2m::kBiasP[i][plan.value_bytes - 1]; q.k.bias_q[i] = crt2m::kBiasQ[i][plan.value_bytes - 1];
+      for (int w = 0; w < 3; ++w) { q.k.w_re[i][w] = crt2m::kByteWeight[i][w]; q.k.w_im_p[i][w] = crt2m::kByteWeightMinusI[i][w]; q.k.w_im_q[i][w] = crt2m::kByteWeightPlusI[i][w]; }
+    }
+    q.A = A; q.lda = lda; q.vexp = vexp; q.W = W;
+    q.part_pitch = ldk; q.col_pitch = ldk * 2; q.plane_pitch = q.col_pitch * n;
+    q.rows = rows; q.ldk = int(ldk); q.n = n; q.moduli = plan.moduli; q.value_bytes = plan.value_bytes;
+    q.op = op == 'T' ? 1 : op == 'C' ? 2 : 0;
+    ProfileScope prof(stream, KernelKind::Quantize);
+    count_launch();
+    switch (int(atype)) {
+      case HYACIN_F64_COMPLEX: launch_2m_typed<double>(stream, q); break;
+      case HYACIN_F32_COMPLEX: launch_2m_typed<float>(stream, q); break;
+      default: launch_2m_typed<__half>(stream, q); break;
+    }
+    HYB_CUDA(cudaGetLastError());
+    return;
+  }
   QuantParams p;
   for (int i = 0; i < crt::kMaxModuli; ++i) {   // the bias depends on the byte width of the values
     p.k.modulus[i] = crt::kModulus[i]; p.k.magic[i] = crt::kMagicCeil[i];

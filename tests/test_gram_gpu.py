@@ -322,3 +322,49 @@ def test_limb_route_equals_reference_limb_route(hy, ref, atype, m, n, eps, ref_a
     assert hy.status() == 0
     assert torch.equal(out["limbs"], out["crt"])
     assert torch.equal(out["limbs"], out["ref"])
+
+
+@pytest.mark.parametrize("atype,op,m,n,corr", [
+    (api.F64_COMPLEX, "N", 66000, 160, 7),      # two row chunks accumulate modulo m; moduli with a square root of -1
+    (api.F64_COMPLEX, "C", 1500, 520, 7),       # conjugate-transposed storage, more than one tile row and column
+    (api.F32_COMPLEX, "T", 900, 130, 7),
+    (api.F64_COMPLEX, "N", 1200, 96, 33),       # 73-bit values: beyond the range of that moduli set, three-part route
+])
+def test_complex_integer_gram_on_both_crt_routes(hy, atype, op, m, n, corr):
+    """Complex input: the sqrt(-1)-moduli route (two planes, one product over all tiles) and, for bit budgets
+    it cannot hold, the three-part route give the oracle's packed integer Gram bit for bit."""
+    torch = _torch()
+    rng = np.random.default_rng(5000 + m + n)
+    A = random_matrix(rng, m, n, atype, col_scale_decades=2.0, zero_cols=(1,))
+    if op == "C":
+        stored = np.ascontiguousarray(A.conj().T)
+    elif op == "T":
+        stored = np.ascontiguousarray(A.T)
+    else:
+        stored = A
+    eps = _eps_for(atype)
+    u, cp, lp, tri = O.herk_init(eps, m, n, atype, corr)
+    Ao = _oracle_input(A, atype)
+    segs = O.segments(m)
+    want_vexp = O.column_exponents(Ao, atype, u, *segs)
+    want_C = O.gram_exact(Ao, atype, want_vexp[0], lp)
+    dA = to_device_colmajor(stored, atype=atype)
+    vexp = torch.from_numpy(want_vexp).cuda()
+    C = torch.full((cp * lp, tri), 0x5555555555555555, dtype=torch.int64, device="cuda")
+    if op == "N":
+        hy.herk_batch(segs[0], segs[1], segs[2], n, atype, dA, m, u, vexp, 0, lp, C)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(C.cpu().numpy().view(np.uint64), want_C)
+    else:
+        # transposed storage goes through the fit (the stage call takes the 'N' layout only): compare ranks and
+        # singular values of the fit on the stored matrix with the fit on an explicit copy
+        k = min(n, 64)
+        S1 = torch.zeros(k, dtype=torch.float64 if (atype & ~1) == api.F64 else torch.float32, device="cuda")
+        S2 = torch.zeros_like(S1)
+        V1 = torch.zeros((k, 2 * n), dtype=S1.dtype, device="cuda"); V2 = torch.zeros_like(V1)
+        r1 = hy.tsvd_fit(eps, op, m, n, k, dA, n, S1, V1, n, m, atype)
+        dN = to_device_colmajor(A, atype=atype)
+        r2 = hy.tsvd_fit(eps, "N", m, n, k, dN, m, S2, V2, n, m, atype)
+        torch.cuda.synchronize()
+        assert r1 == r2 and torch.equal(S1, S2) and torch.equal(V1, V2)
+    assert hy.status() == 0
