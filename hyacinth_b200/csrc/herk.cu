@@ -76,8 +76,14 @@ static void herk_crt(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPr
   cudaStream_t stream = handle->cudaStream;
   const int cplx = is_complex(atype), parts = cplx ? 3 : 1;
   const int64_t tri = (int64_t(n) * n + n) / 2;
-  const CrtPlan plan = make_crt_plan(u, cplx, rows);
+  CrtPlan plan = make_crt_plan(u, cplx, rows);
   if (plan.moduli == 0) return;
+  {
+    // keep the residue planes of one chunk within about 8 GiB whatever N and the number of moduli are
+    const int64_t per_row = int64_t(plan.two_m ? 2 : parts) * n * plan.moduli;
+    const int64_t cap_rows = std::max<int64_t>(8 * kStageK, ((int64_t(8) << 30) / per_row) / kStageK * kStageK);
+    plan.chunk_rows = int(std::min<int64_t>(plan.chunk_rows, cap_rows));
+  }
   const TilePlan tp = make_tile_plan(n);
   const size_t elem = (base_type(atype) == HYACIN_F64 ? 8 : base_type(atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);
   if (plan.two_m) {
@@ -195,6 +201,11 @@ static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows);
 void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
               int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
   const int cplx = is_complex(atype);
+  if (n > 65535) {
+    // launch grids index columns with a 16-bit block coordinate; a Gram of that size (> 68 GB of limbs) is out of reach anyway
+    std::fprintf(stderr, "hyacin-b200: N = %d exceeds the supported 65535 columns; nothing computed\n", n);
+    return;
+  }
   if (rows <= 0 || u < 0) {
     // Nothing to add: an overwrite still has to define C (src/hyacin_herk.cpp:287).
     if (beta == 0) {
