@@ -69,7 +69,16 @@ template <> struct Real<DD> {
   static __device__ __forceinline__ DD add(DD a, DD b) { return dd_add(a, b); }
   static __device__ __forceinline__ DD sub(DD a, DD b) { return dd_sub(a, b); }
   static __device__ __forceinline__ DD neg(DD a) { return DD{-a.x, -a.y}; }
-  static __device__ __forceinline__ DD fnma(DD a, DD b, DD c) { return dd_sub(c, dd_mul(a, b)); }
+  // c - a b in one pass: exact leading product (p, e), cross terms folded into e, one two-sum for the leading
+  // difference, one renormalisation at the end (15 operations against 19 for a product followed by a subtraction)
+  static __device__ __forceinline__ DD fnma(DD a, DD b, DD c) {
+    const double p = a.x * b.x;
+    double e = fma(a.x, b.x, -p);
+    e = fma(a.x, b.y, e); e = fma(a.y, b.x, e);
+    const double s = c.x - p, bb = s - c.x;
+    const double err = (c.x - (s - bb)) - (p + bb);
+    return dd_renorm(s, (c.y - e) + err);
+  }
   static __device__ __forceinline__ bool less(DD a, DD b) { return a.x < b.x || (a.x == b.x && a.y < b.y); }
   static __device__ __forceinline__ double to_double(DD a) { return a.x; }
   // 1/sqrt(a) to double-double accuracy: two Newton steps y <- y (3/2 - a y^2 / 2) from the double estimate.
