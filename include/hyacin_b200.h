@@ -22,7 +22,10 @@ uint32_t hyacinB200Status(int32_t clear);
 
 /* Schedule of one hyacinXherkBatch call with `rows` local rows and quantisation bits u: number of CRT
  * moduli, bytes per biased quantised value, rows reconstructed together, rows per kernel launch.
- * Takes over the role of the reference's cost model (src/hyacin_herk.cpp:11-43) for this build. */
+ * Takes over the role of the reference's cost model (src/hyacin_herk.cpp:11-43) for this build.
+ * Describes the schedule these stage hooks work with; for complex input hyacinXherkBatch itself prefers a
+ * second moduli set with a square root of -1 (two planes per column, one product over all tiles) whenever
+ * that set covers the bit budget, which this query does not report. */
 void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int32_t* moduli, int32_t* valueBytes,
                        int32_t* groupRows, int32_t* chunkRows);
 
