@@ -22,6 +22,7 @@
 #include "ptx_sm100.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <cstdlib>
 
 namespace hyb {
 namespace {
@@ -240,6 +241,188 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// ---- two-CTA variant (residue Gram over the upper triangle) ---------------------------------------------------
+// A CTA pair (cluster of two, the two SMs of a TPC) works on a 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA
+// stages its 128 rows of the A operand and its 128 columns of the B operand, the MMA issued by the even CTA reads
+// both halves, and each CTA keeps the accumulator of its own 128 rows in its tensor memory.  Per MMA every SM
+// fetches and reads 8 KiB of operands instead of 12, which is what matters when the step runs into the power cap.
+// Loads are plain TMA tile loads of the CTA's own halves that signal the even CTA's barrier (no multicast);
+// tcgen05.commit arrives on the barriers of both CTAs.  The output layout is unchanged: the pair tile (TY, TX)
+// is the two ordinary tiles (2 TY, TX) and (2 TY + 1, TX).
+constexpr int kStages2 = 6;
+constexpr uint32_t kStageBytes2 = 2 * kABytes;               // 16 KiB of A rows + 16 KiB of B columns per CTA
+constexpr size_t kSmemBytes2 = 1024 + size_t(kStages2) * kStageBytes2 + 256;
+constexpr uint32_t kInstrDesc2 = (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(256 >> 3) << 17) | (uint32_t(256 >> 4) << 24);
+struct Barriers2 {
+  uint64_t full[kStages2], empty[kStages2], acc_full[2], acc_empty[2];
+  uint32_t tmem_base; uint32_t abort_flag;
+};
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {      // arrives on this barrier in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(uint16_t(3)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void pair_tile_coords(int tiles_x, int t, int* TY, int* TX) {   // TY <= TX, column-block major
+  int x = 0, base = 0;
+  for (;;) { if (t < base + x + 1 || x + 1 >= tiles_x) { *TY = t - base; *TX = x; return; } base += x + 1; ++x; }
+}
+__device__ __forceinline__ int tile_index(int tiles_y, int ty, int tx) {                   // inverse of tile_coords
+  int base = 0;
+  for (int x = 0; x < tx; ++x) { int cnt = 2 * x + 2; base += cnt > tiles_y ? tiles_y : cnt; }
+  return base + ty;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gram_pair_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p, int tiles_x) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  Barriers2* bars = reinterpret_cast<Barriers2*>(aligned + size_t(kStages2) * kStageBytes2);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int pair_rows = (p.tiles_y + 1) / 2;                            // pair tiles per column block when every tile is wanted
+  const int pairs = p.full ? pair_rows * tiles_x : tiles_x * (tiles_x + 1) / 2;
+  const int num_items = p.moduli * pairs;
+  auto pair_of = [&](int t, int* TY, int* TX) {
+    if (p.full) { *TX = t / pair_rows; *TY = t - *TX * pair_rows; } else pair_tile_coords(tiles_x, t, TY, TX);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&bars->acc_full[a], 1); mbar_init(&bars->acc_empty[a], 2 * kEpilogueWarps); }
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // barriers and tensor memory of both CTAs exist from here on
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs: own halves, completion counted on the even CTA's barrier) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0; bool ok = true;
+      for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+        const int m = item / pairs; int TY, TX; pair_of(item - m * pairs, &TY, &TX);
+        const int y0 = (2 * TY + int(rank)) * kTileY, x0 = TX * kTileX + int(rank) * kTileY;
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 11u))) break;
+          if (rank == 0) mbar_expect_tx(&bars->full[stage], 2 * kStageBytes2);
+          const uint32_t sa = base + stage * kStageBytes2, sb = sa + kABytes;
+          const uint32_t full0 = map_to_cta(smem_u32(&bars->full[stage]), 0);
+          tma_load_3d_pair(sa, &tmap, full0, p.ka0 + kb * kStageK, y0, m);
+          tma_load_3d_pair(sb, &tmap, full0, p.kb0 + kb * kStageK, x0, m);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0; bool ok = true;
+      for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+        if (!(ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 12u))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileX;
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->full[stage], phase, abort_flag, p.status, 13u))) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * kStageBytes2, sb = sa + kABytes;
+          const uint64_t adesc = smem_desc_k128(sa), bdesc = smem_desc_k128(sb);
+#pragma unroll
+          for (int k = 0; k < kStageK / kUmmaK; ++k)
+            umma_i8_pair(tmem_d, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), kInstrDesc2, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&bars->empty[stage]);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&bars->acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps (both CTAs: own 128 rows) ----------------
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;
+    uint32_t acc = 0, acc_phase = 0; bool ok = true;
+    for (int item = cluster_id; item < num_items && ok; item += num_clusters) {
+      const int m = item / pairs; int TY, TX; pair_of(item - m * pairs, &TY, &TX);
+      const int ty = 2 * TY + int(rank);
+      ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status, 14u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (ty < p.tiles_y) {
+        const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
+        const int tile = p.full ? ty + TX * p.tiles_y : tile_index(p.tiles_y, ty, TX);
+        const uint32_t modulus = p.k.modulus[m], magic = p.k.magic[m], bias = p.k.bias[m];
+        uint8_t* out = p.residues + (size_t(m) * p.num_tiles + tile) * size_t(kTileY * kTileX) + size_t(row) * kTileX;
+#pragma unroll 1
+        for (int c = 0; c < kTileX / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          uint4 old0 = make_uint4(0, 0, 0, 0), old1 = old0;
+          if (p.accumulate) { old0 = *reinterpret_cast<const uint4*>(out + c * 32); old1 = *reinterpret_cast<const uint4*>(out + c * 32 + 16); }
+          tmem_ld_wait();
+          const uint32_t oldw[8] = {old0.x, old0.y, old0.z, old0.w, old1.x, old1.y, old1.z, old1.w};
+          uint32_t packed[8];
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              uint32_t t = v[w * 4 + b] + bias + ((oldw[w] >> (8 * b)) & 0xFFu);
+              uint32_t r = t - __umulhi(t, magic) * modulus;
+              r = r >= modulus ? r - modulus : r;
+              word |= r << (8 * b);
+            }
+            packed[w] = word;
+          }
+          *reinterpret_cast<uint4*>(out + c * 32) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(out + c * 32 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // Teardown: every role of both CTAs ends up here, also after an expired wait.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 }  // namespace
 
@@ -294,6 +477,17 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
     const uint32_t m = !have ? 1u : g.table == 0 ? crt::kModulus[i] : crt2m::kModulus[i];
     p.k.modulus[i] = m; p.k.magic[i] = !have ? 0u : g.table == 0 ? crt::kMagicFloor[i] : crt2m::kMagicFloor[i];
     p.k.bias[i] = (0x80000000u / m) * m;
+  }
+  if (p.num_kblocks > 0 && g.sm_count >= 2) {
+    // CTA pairs on 256 x 256 tiles; the single-CTA kernel below remains for devices that report one SM
+    HYB_CUDA(cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes2)));
+    const int pairs = p.full ? ((tp.tiles_y + 1) / 2) * tp.tiles_x : tp.tiles_x * (tp.tiles_x + 1) / 2;
+    int clusters = g.sm_count / 2; if (clusters > g.moduli * pairs) clusters = g.moduli * pairs;
+    ProfileScope prof(stream, KernelKind::Gram);
+    count_launch();
+    gram_pair_kernel<<<2 * clusters, kThreads, kSmemBytes2, stream>>>(tmap, p, tp.tiles_x);
+    HYB_CUDA(cudaGetLastError());
+    return;
   }
   HYB_CUDA(cudaFuncSetAttribute(gram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
   const int items = g.moduli * p.num_tiles;
