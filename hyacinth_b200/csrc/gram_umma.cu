@@ -5,7 +5,10 @@
 // reduction is the epilogue of the GEMM tile, so the only thing that leaves the SM is one byte per
 // (entry, modulus).
 //
-// Structure (one CTA per SM, persistent over (modulus, tile) work items):
+// Two kernels.  gram_pair_kernel (further down) is the one the CRT route runs: clusters of two CTAs on 256 x 256
+// tiles with tcgen05.mma.cta_group::2.  gram_kernel<LIMBS> is the single-CTA form (128 x 256 tiles); it carries
+// the limb route and is the fallback of the CRT route.  Structure of the single-CTA form (one CTA per SM,
+// persistent over (modulus, tile) work items):
 //   warp 0     TMA producer: 128-byte-swizzled K-major boxes of the A operand (128 Gram rows) and the B
 //              operand (256 Gram columns) into a 4-stage shared-memory ring, completion on mbarriers;
 //   warp 1     MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M128 N256 K32) on shared-memory
@@ -14,8 +17,9 @@
 //   warps 2-5  epilogue: tcgen05.ld of the int32 accumulator (32 lanes x 32 columns per load), reduction
 //              modulo m, optional accumulation onto the residues of earlier row chunks, 32-byte stores.
 // The two TMEM buffers let the epilogue of one tile overlap the main loop of the next.
-// No TMA load in this file uses cluster multicast.  Every wait is bounded: a wait that expires raises a
-// status word for the host and makes all roles leave their loops so that TMEM is still released.
+// No TMA load in this file uses cluster multicast (tcgen05.commit of the pair kernel does address both CTAs of
+// its pair).  Every wait is bounded: a wait that expires raises a status word for the host and makes all roles
+// leave their loops so that TMEM is still released.
 #include "hyb_internal.h"
 #include "crt_tables.h"
 #include "limbs192.cuh"
@@ -478,7 +482,8 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
     p.k.modulus[i] = m; p.k.magic[i] = !have ? 0u : g.table == 0 ? crt::kMagicFloor[i] : crt2m::kMagicFloor[i];
     p.k.bias[i] = (0x80000000u / m) * m;
   }
-  if (p.num_kblocks > 0 && g.sm_count >= 2) {
+  static const bool single_cta = [] { const char* e = std::getenv("HYACIN_B200_GRAM_SINGLE_CTA"); return e && e[0] == '1'; }();   // diagnosis: A/B the two kernels
+  if (!single_cta && p.num_kblocks > 0 && g.sm_count >= 2) {
     // CTA pairs on 256 x 256 tiles; the single-CTA kernel below remains for devices that report one SM
     HYB_CUDA(cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes2)));
     const int pairs = p.full ? ((tp.tiles_y + 1) / 2) * tp.tiles_x : tp.tiles_x * (tp.tiles_x + 1) / 2;
