@@ -166,6 +166,9 @@ def emit_set(emit, ns, prefix, mods, complex_set):
     emit(f"#define {prefix}_INV_INIT {{ " + ", ".join(inv_rows) + " }")
     emit(f"#define {prefix}_PRODUCT_INIT {{ " + ", ".join(prod_rows) + " }")
     emit(f"#define {prefix}_HALF_PRODUCT_INIT {{ " + ", ".join(half_rows) + " }")
+    emit("// Smallest multiple of each modulus above 255: added before subtracting a Garner digit (a byte) so that the")
+    emit("// difference stays positive.")
+    emit(f"#define {prefix}_LIFT_INIT {{ " + ", ".join(str((255 // m + 1) * m) for m in mods) + " }")
     if complex_set:
         emit(f"#define {prefix}_INV_TWO_INIT {{ " + ", ".join(str(pow(2, -1, m)) for m in mods) + " }")
         emit(f"#define {prefix}_INV_TWO_IOTA_INIT {{ " + ", ".join(str(pow(2 * iota[m], -1, m)) for m in mods) + " }")

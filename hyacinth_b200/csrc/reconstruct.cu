@@ -25,12 +25,14 @@ __constant__ uint32_t c_magic[crt::kMaxModuli] = HYB_CRT_MAGIC_CEIL_INIT;
 __constant__ uint8_t c_inv[crt::kMaxModuli][crt::kMaxModuli] = HYB_CRT_INV_INIT;
 __constant__ uint64_t c_product[crt::kMaxModuli][3] = HYB_CRT_PRODUCT_INIT;
 __constant__ uint64_t c_half_product[crt::kMaxModuli][3] = HYB_CRT_HALF_PRODUCT_INIT;
+__constant__ uint16_t c_lift[crt::kMaxModuli] = HYB_CRT_LIFT_INIT;
 // the same for the moduli of complex input (crt2m); padded to the size of the first set
 __constant__ uint16_t c2_modulus[crt::kMaxModuli] = HYB_CRT2M_MODULUS_INIT;
 __constant__ uint32_t c2_magic[crt::kMaxModuli] = HYB_CRT2M_MAGIC_CEIL_INIT;
 __constant__ uint8_t c2_inv[crt::kMaxModuli][crt::kMaxModuli] = HYB_CRT2M_INV_INIT;
 __constant__ uint64_t c2_product[crt::kMaxModuli][3] = HYB_CRT2M_PRODUCT_INIT;
 __constant__ uint64_t c2_half_product[crt::kMaxModuli][3] = HYB_CRT2M_HALF_PRODUCT_INIT;
+__constant__ uint16_t c2_lift[crt::kMaxModuli] = HYB_CRT2M_LIFT_INIT;
 __constant__ uint16_t c2_inv_two[crt::kMaxModuli] = HYB_CRT2M_INV_TWO_INIT;
 __constant__ uint16_t c2_inv_two_iota[crt::kMaxModuli] = HYB_CRT2M_INV_TWO_IOTA_INIT;
 static_assert(crt2m::kMaxModuli <= crt::kMaxModuli, "crt2m tables are stored in arrays sized for crt");
@@ -39,6 +41,7 @@ template <int SET> struct Tables;
 template <> struct Tables<0> {
   static __device__ __forceinline__ uint32_t modulus(int i) { return c_modulus[i]; }
   static __device__ __forceinline__ uint32_t magic(int i) { return c_magic[i]; }
+  static __device__ __forceinline__ uint32_t lift(int i) { return c_lift[i]; }
   static __device__ __forceinline__ uint32_t inv(int j, int i) { return c_inv[j][i]; }
   static __device__ __forceinline__ const uint64_t (&product(int k))[3] { return c_product[k]; }
   static __device__ __forceinline__ const uint64_t (&half_product(int k))[3] { return c_half_product[k]; }
@@ -46,6 +49,7 @@ template <> struct Tables<0> {
 template <> struct Tables<1> {
   static __device__ __forceinline__ uint32_t modulus(int i) { return c2_modulus[i]; }
   static __device__ __forceinline__ uint32_t magic(int i) { return c2_magic[i]; }
+  static __device__ __forceinline__ uint32_t lift(int i) { return c2_lift[i]; }
   static __device__ __forceinline__ uint32_t inv(int j, int i) { return c2_inv[j][i]; }
   static __device__ __forceinline__ const uint64_t (&product(int k))[3] { return c2_product[k]; }
   static __device__ __forceinline__ const uint64_t (&half_product(int k))[3] { return c2_half_product[k]; }
@@ -92,7 +96,7 @@ reconstruct_kernel(int n, int k, int tiles_y, int num_tiles, const uint8_t* __re
         if (i < k) {
           uint32_t t = r[i][w] & 0xFFu; r[i][w] >>= 8;
           const uint32_t mi = Tb::modulus(i), magic = Tb::magic(i);
-          const uint32_t lift = (255u / mi + 1u) * mi;                 // multiple of m_i above every digit a_j <= 255
+          const uint32_t lift = Tb::lift(i);                           // multiple of m_i above every digit a_j <= 255
 #pragma unroll
           for (int j = 0; j < i; ++j) {
             // (t - a_j) * m_j^-1 mod m_i; the lift keeps the difference positive, the product stays below 2^18
