@@ -491,8 +491,9 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
     ProfileScope prof(stream, KernelKind::Gram);
     count_launch();
     gram_pair_kernel<<<2 * clusters, kThreads, kSmemBytes2, stream>>>(tmap, p, tp.tiles_x);
-    HYB_CUDA(cudaGetLastError());
-    return;
+    const cudaError_t launched = cudaGetLastError();
+    if (launched == cudaSuccess) return;
+    std::fprintf(stderr, "hyacin-b200: cluster launch of the pair Gram kernel refused (%s); using the single-CTA kernel\n", cudaGetErrorString(launched));
   }
   HYB_CUDA(cudaFuncSetAttribute(gram_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
   const int items = g.moduli * p.num_tiles;
