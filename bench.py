@@ -263,7 +263,14 @@ def main():
     # ---------------- e2e: host matrix -> hyacinTsvdFit -> host results, every step ----------------
     e2e = None
     if not args.no_e2e and not args.no_fit:
-        host_budget = 144 * (1 << 30) // world                      # pinned bytes this rank may hold
+        # pinned bytes this rank may hold: at most half of what the host has free, split over the ranks
+        try:
+            import psutil
+            free_host = float(psutil.virtual_memory().available)
+        except Exception:
+            free_host = float(96 << 30)
+        free_host = -max_over_ranks(-free_host)                      # the same figure on every rank
+        host_budget = int(min(144 * (1 << 30), 0.5 * free_host)) // world
         host_rows = rows
         while host_rows * n * 8 > host_budget and host_rows > 1024:
             host_rows //= 2
