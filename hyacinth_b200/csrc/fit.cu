@@ -147,7 +147,7 @@ bool build_gram(const hyacinHandle_t* h, double eps, char op, int M, int N, hyac
     launch_column_exponents(h->cudaStream, type, batches, seg, lastM, N, A, lda, u, vexp, op);
     hyacinAllReduceVExp(h, uint64_t(N), vexp);
     timer_mark(h, Segment::Distributed);
-    if (lp > 0) herk_any(h, M, N, type, A, lda, op, u, vexp, 0, lp, C);
+    if (lp > 0) herk_any(h, M, N, type, A, lda, op, u, vexp, 0, lp, C, batches, seg);
   } else {
     hyacinXquantizeScaleBatch(h, batches, seg, lastM, N, type, A, lda, u, vexp);
     hyacinAllReduceVExp(h, uint64_t(N), vexp);

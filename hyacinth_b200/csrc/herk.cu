@@ -12,6 +12,7 @@
 #include "crt_tables.h"
 #include <hyacin_b200.h>
 #include <algorithm>
+#include <vector>
 #include <climits>
 #include <cmath>
 
@@ -198,8 +199,81 @@ static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacin
 static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows);
 
 // Integer Gram of op(A) (rows x n): the body of hyacinXherkBatch, with the transposed layouts the fits pass in.
+static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows);
+
+static void herk_rows(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
+                      int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
+  const int cplx = is_complex(atype);
+  if (use_limb_route(handle->GramMatrixAlgorithm, u, cplx, rows)) herk_limbs(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
+  else herk_crt(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
+}
+
+// Precision ladder over row segments (reference: src/fp_exponent.cu:67-76 and the bucketing of
+// src/hyacin_herk.cpp:316-338): a segment whose column maxima all lie d bits below the global ones only holds
+// values |q| <= 2^(u - d), so its share of the Gram needs fewer moduli (or digit planes) and fewer bytes per value;
+// a segment of zeros needs nothing.  The bits per segment come back through one small device-to-host copy (the
+// reference has the same pipeline bubble).  Consecutive segments of one precision level form a run; every run
+// is an independent exact contribution added with beta = 1, so the result does not depend on the split.
+// Returns false when there is nothing to gain (every segment at the top level), and the caller runs the plain path.
+static bool herk_ladder(const hyacinHandle_t* handle, int64_t rows, int batches, int64_t seg_m, int n, hyacinPrecision_t atype,
+                        const void* A, int64_t lda, char op, int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
+  const int cplx = is_complex(atype);
+  cudaStream_t stream = handle->cudaStream;
+  int32_t* seg_dev = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&seg_dev), size_t(batches) * sizeof(int32_t), handle->mempool, stream));
+  if (!seg_dev) return false;
+  std::vector<int32_t> seg_u(batches);
+  launch_vector_range(stream, batches, n, u, vexp, seg_dev);
+  HYB_CUDA(cudaMemcpyAsync(seg_u.data(), seg_dev, size_t(batches) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+  HYB_CUDA(cudaStreamSynchronize(stream));
+  HYB_CUDA(cudaFreeAsync(seg_dev, stream));
+  // precision level of a segment: 0 = nothing to do, otherwise the bit budget rounded up to a multiple of 8 (one
+  // value byte, about one modulus per 4 bits); the top level is that of u itself
+  auto level_of = [&](int32_t bits) { return bits < 0 ? 0 : std::min((bits + 8) / 8, (u + 8) / 8); };
+  const int top = level_of(u);
+  struct Run { int64_t row0, rows; int level, bits; };
+  std::vector<Run> runs;
+  bool gain = false;
+  for (int b = 0; b < batches; ++b) {
+    const int64_t r0 = int64_t(b) * seg_m, r1 = std::min<int64_t>(rows, r0 + seg_m);
+    if (r1 <= r0) break;
+    const int32_t bits = seg_u[b] == INT_MIN ? -1 : std::min<int32_t>(seg_u[b], u);
+    const int level = level_of(bits);
+    if (level < top) gain = true;
+    if (!runs.empty() && runs.back().level == level) { runs.back().rows += r1 - r0; runs.back().bits = std::max(runs.back().bits, int(bits)); }
+    else runs.push_back(Run{r0, r1 - r0, level, int(bits)});
+  }
+  if (!gain || runs.size() > 16) return false;               // nothing to save, or too fragmented to be worth a reconstruction per run
+  {
+    // Worth it?  Work is counted in rows x moduli; every extra run costs one more reconstruction, about as much as
+    // 100 000 row-moduli of quantisation and Gram.
+    const int k_top = make_crt_plan(u, cplx, rows).moduli;
+    int64_t saved = 0; int executed = 0;
+    for (const Run& r : runs) {
+      const int k_run = r.level == 0 ? 0 : make_crt_plan(std::max(r.bits, 0), cplx, r.rows).moduli;
+      saved += r.rows * int64_t(std::max(0, k_top - k_run));
+      executed += r.level != 0;
+    }
+    if (saved <= int64_t(100000) * std::max(0, executed - 1)) return false;
+  }
+  const size_t elem = (base_type(atype) == HYACIN_F64 ? 8 : base_type(atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);
+  bool any = false;
+  for (const Run& r : runs) {
+    if (r.level == 0) continue;
+    const char* src = static_cast<const char*>(A) + size_t(r.row0) * elem * (op == 'N' ? 1 : size_t(lda));
+    herk_rows(handle, r.rows, n, atype, src, lda, op, std::max(r.bits, 0), vexp, (beta || any) ? 1 : 0, order_c, C);
+    any = true;
+  }
+  if (!any && beta == 0) {
+    const uint64_t tri = (uint64_t(n) * n + n) / 2;
+    HYB_CUDA(cudaMemsetAsync(C, 0, tri * uint64_t(order_c) * (1 + cplx) * sizeof(uint64_t), stream));
+  }
+  if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "I8I32-LADDER [segments=%d] [runs=%d] [top-bits=%d]\n", batches, int(runs.size()), u);
+  return true;
+}
+
 void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
-              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C) {
+              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C, int batches, int64_t seg_m) {
   const int cplx = is_complex(atype);
   if (n > 65535) {
     // launch grids index columns with a 16-bit block coordinate; a Gram of that size (> 68 GB of limbs) is out of reach anyway
@@ -214,8 +288,8 @@ void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision
     }
     return;
   }
-  if (use_limb_route(handle->GramMatrixAlgorithm, u, cplx, rows)) herk_limbs(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
-  else herk_crt(handle, rows, n, atype, A, lda, op, u, vexp, beta ? 1 : 0, order_c, C);
+  if (batches > 1 && seg_m > 0 && herk_ladder(handle, rows, batches, seg_m, n, atype, A, lda, op, u, vexp, beta, order_c, C)) return;
+  herk_rows(handle, rows, n, atype, A, lda, op, u, vexp, beta, order_c, C);
 }
 
 static bool use_limb_route(char algorithm, int u, int cplx, int64_t rows) {
@@ -257,7 +331,7 @@ extern "C" void hyacinXherkBatch(const hyacinHandle_t* handle, int32_t batches, 
   if (int(Atype) < 0 || int(Atype) > int(HYACIN_F16_COMPLEX)) return;
   hyb::timer_mark(handle, hyb::Segment::Distributed);
   const int64_t rows = batches <= 1 ? int64_t(lastM) : int64_t(batches - 1) * segM + lastM;
-  hyb::herk_any(handle, rows, N, Atype, A, lda, 'N', u, vexp, beta, orderC, C);
+  hyb::herk_any(handle, rows, N, Atype, A, lda, 'N', u, vexp, beta, orderC, C, batches, segM);
 }
 
 extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,

@@ -68,8 +68,10 @@ __host__ __device__ inline void tile_coords(int n_tiles_y, int t, int* ty, int* 
 }
 
 // Integer Gram of op(A): what hyacinXherkBatch does, for any of the three input layouts.
+// batches / seg_m: the row segmentation vexp was built with (rows 1.. of vexp hold the per-segment exponents); with
+// more than one segment the precision ladder may split the rows into runs of lower precision.
 void herk_any(const hyacinHandle_t* handle, int64_t rows, int n, hyacinPrecision_t atype, const void* A, int64_t lda, char op,
-              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C);
+              int u, const int32_t* vexp, int beta, int order_c, uint64_t* C, int batches = 1, int64_t seg_m = 0);
 
 // Plan of one hyacinXherkBatch call: how many moduli, how rows are grouped and chunked.
 struct CrtPlan {

@@ -368,3 +368,30 @@ def test_complex_integer_gram_on_both_crt_routes(hy, atype, op, m, n, corr):
         torch.cuda.synchronize()
         assert r1 == r2 and torch.equal(S1, S2) and torch.equal(V1, V2)
     assert hy.status() == 0
+
+
+@pytest.mark.parametrize("atype,spread,zero_block", [(api.F64, 12.0, False), (api.F64, 0.0, True), (api.F32_COMPLEX, 0.0, True)])
+def test_precision_ladder_over_row_segments_is_exact(hy, atype, spread, zero_block):
+    """Row segments far below the column maxima (or all zero) go through cheaper runs; the integer Gram is unchanged."""
+    rng = np.random.default_rng(99)
+    m, n, seg_k = 120000, 96, 8192
+    A = random_matrix(rng, m, n, atype, col_scale_decades=1.0, spread_rows=spread)
+    if zero_block:
+        A[3 * seg_k:7 * seg_k] = 0                     # four all-zero segments in the middle
+        A[10 * seg_k:] *= 1e-5                         # and a tail seventeen bits below the column maxima
+    dA = to_device_colmajor(A, atype=atype)
+    eps = _eps_for(atype)
+    u, cp, lp, tri = hy.herk_batch_init(eps, m, n, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u, seg_k)
+    assert segs[0] > 1
+    Ao = _oracle_input(A, atype)
+    want_vexp = O.column_exponents(Ao, atype, u, *segs)
+    np.testing.assert_array_equal(vexp.cpu().numpy(), want_vexp)
+    hy.launch_count(reset=True)
+    C = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
+    used = hy.launch_count(reset=True)
+    want_C = O.gram_exact(Ao, atype, want_vexp[0], lp)
+    np.testing.assert_array_equal(C.cpu().numpy().view(np.uint64), want_C)
+    # the plain schedule needs two chunks (quantise + Gram each) and one reconstruction per panel; the ladder adds the
+    # segment scan and one reconstruction per run
+    assert used >= 8, used
