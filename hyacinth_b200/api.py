@@ -31,6 +31,7 @@ B200_SYMBOLS = [
     "hyacinB200Status", "hyacinB200CrtPlan", "hyacinB200TileInfo", "hyacinB200QuantizeCrt",
     "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
     "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic", "hyacinB200QuantizeLimbs", "hyacinB200GramLimbs",
+    "hyacinB200DequantizeViaSlices",
 ]
 
 
@@ -80,6 +81,7 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200GramResidues": (None, [H, i32, i32, vp, i64, i64, i32, i32, i32, i32, vp]),
         "hyacinB200Reconstruct": (None, [H, i32, i32, vp, i32, i32, vp]),
         "hyacinB200SlicePlan": (None, [i32, i32, POINTER(i32), POINTER(i32)]),
+        "hyacinB200DequantizeViaSlices": (None, [H, i32, i32, vp, vp, i32, i32, POINTER(i32), vp, i32]),
         "hyacinB200HerkBatchStatic": (i32, [H, i32, i32, i32, i32, i32, vp, i32, i32, vp, i32, i32, vp]),
         "hyacinB200QuantizeLimbs": (None, [H, i32, i32, i32, vp, i32, vp, i32, vp, i64]),
         "hyacinB200GramLimbs": (None, [H, i32, i32, vp, i64, i64, i32, i32, i32, i32, i32, vp]),
@@ -230,6 +232,12 @@ class Hyacin:
 
     def gram_limbs(self, n, order, W, ldw, plane_stride, ka0, kb0, k_rows, beta, order_c, C):
         self.lib.hyacinB200GramLimbs(byref(self.h), n, order, _dp(W), ldw, plane_stride, ka0, kb0, k_rows, beta, order_c, _dp(C))
+
+    def dequantize_via_slices(self, n, order_c, C, vexp, atype, ranks, G, ldg):
+        """Gram format and matrix from the slices `ranks` ranks would exchange (the fits' post-collective route)."""
+        g = c_int32()
+        self.lib.hyacinB200DequantizeViaSlices(byref(self.h), n, order_c, _dp(C), _dp(vexp), atype, ranks, byref(g), _dp(G), ldg)
+        return g.value
 
     def reconstruct(self, n, moduli, residues, beta, order_c, C):
         self.lib.hyacinB200Reconstruct(byref(self.h), n, moduli, _dp(residues), beta, order_c, _dp(C))

@@ -10,15 +10,13 @@
 // case.  Integer addition is associative, so the result does not depend on rank order or on the algorithm
 // NCCL picks (ring, tree or in-switch reduction).
 #include "hyb_internal.h"
+#include "slices.cuh"
 #include <hyacin_b200.h>
 
 namespace hyb {
 
-struct SlicePlan { int slices; int width; };
-
-// Slices 0 .. slices-2 hold `width` unsigned bits each, the last one the remaining (signed) top bits.
 // A value of `order` limbs has at most 63 * order + 1 significant bits including its sign.
-static SlicePlan slice_plan(int order, int ranks) {
+SlicePlan slice_plan(int order, int ranks) {
   int log_r = 0; while ((int64_t(1) << log_r) < ranks) ++log_r;
   SlicePlan p; p.width = 64 - log_r; if (p.width > 62) p.width = 62;
   const int total = 63 * order + 1;
@@ -30,39 +28,6 @@ static SlicePlan slice_plan(int order, int ranks) {
 }
 
 namespace {
-
-struct W192 { uint64_t w[3]; };
-
-__device__ __forceinline__ W192 load_value(const uint64_t* p, uint64_t stride, int order) {
-  W192 v; const uint64_t a0 = p[0];
-  if (order == 1) { v.w[0] = a0; v.w[1] = v.w[2] = uint64_t(int64_t(a0) >> 63); return v; }
-  const uint64_t a1 = p[stride];
-  if (order == 2) {
-    const uint64_t ext = uint64_t(int64_t(a1) >> 63);
-    v.w[0] = a0 | (a1 << 63); v.w[1] = (a1 >> 1) | (ext << 63); v.w[2] = ext; return v;
-  }
-  const uint64_t a2 = p[2 * stride], ext = uint64_t(int64_t(a2) >> 63);
-  v.w[0] = a0 | (a1 << 63); v.w[1] = (a1 >> 1) | (a2 << 62); v.w[2] = (a2 >> 2) | (ext << 62);
-  return v;
-}
-__device__ __forceinline__ void sar(W192& v, int s) {      // arithmetic shift right, 0 < s < 64
-  const uint64_t ext = uint64_t(int64_t(v.w[2]) >> 63);
-  v.w[0] = (v.w[0] >> s) | (v.w[1] << (64 - s)); v.w[1] = (v.w[1] >> s) | (v.w[2] << (64 - s)); v.w[2] = (v.w[2] >> s) | (ext << (64 - s));
-}
-__device__ __forceinline__ void add_shifted(W192& v, uint64_t s, bool is_signed, int shift) {   // v += s << shift
-  const uint64_t ext = is_signed ? uint64_t(int64_t(s) >> 63) : 0;
-  uint64_t t[3] = {s, ext, ext};
-  const int ws = shift >> 6, bs = shift & 63;
-  uint64_t sh[3];
-#pragma unroll
-  for (int k = 2; k >= 0; --k) {
-    const uint64_t lo = (k - ws >= 0) ? t[k - ws] : 0, below = (k - ws - 1 >= 0) ? t[k - ws - 1] : 0;
-    sh[k] = bs ? (lo << bs) | (below >> (64 - bs)) : lo;
-  }
-  unsigned __int128 c = (unsigned __int128)v.w[0] + sh[0]; v.w[0] = uint64_t(c);
-  c = (unsigned __int128)v.w[1] + sh[1] + uint64_t(c >> 64); v.w[1] = uint64_t(c);
-  v.w[2] = v.w[2] + sh[2] + uint64_t(c >> 64);
-}
 
 __global__ void __launch_bounds__(256)
 limbs_to_slices_kernel(int order, SlicePlan plan, uint64_t count, const uint64_t* __restrict__ A, uint64_t* __restrict__ S) {
@@ -114,9 +79,30 @@ extern "C" void hyacinB200SlicePlan(int32_t orderA, int32_t ranks, int32_t* slic
 }
 
 #ifdef HYACIN_BUILD_NO_NCCL
+namespace hyb { uint64_t* allreduce_to_slices(const hyacinHandle_t*, int, int, uint64_t, const uint64_t*, int*) { return nullptr; } }
 extern "C" void hyacinAllReduce1Drow(const hyacinHandle_t*, int32_t, int32_t, uint64_t, uint64_t*) {}
 extern "C" void hyacinAllReduceVExp(const hyacinHandle_t*, uint64_t, int32_t*) {}
 #else
+
+namespace hyb {
+uint64_t* allreduce_to_slices(const hyacinHandle_t* handle, int panels, int order, uint64_t count, const uint64_t* C, int* ranks_out) {
+  if (panels <= 0 || order <= 0 || order > 3 || count == 0 || handle->ncclComm == nullptr) return nullptr;
+  int ranks = 0;
+  if (ncclCommCount(handle->ncclComm, &ranks) != ncclSuccess || ranks <= 1) return nullptr;
+  timer_mark(handle, Segment::Comm);
+  cudaStream_t stream = handle->cudaStream;
+  const uint64_t words = uint64_t(panels) * uint64_t(slice_count(order, ranks)) * count;
+  uint64_t* S = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&S), words * sizeof(uint64_t), handle->mempool, stream));
+  if (!S) return nullptr;
+  launch_limbs_to_slices(stream, panels, order, ranks, count, C, S);
+  ncclResult_t r = ncclAllReduce(S, S, words, ncclUint64, ncclSum, handle->ncclComm, stream);
+  if (r != ncclSuccess) std::fprintf(stderr, "hyacin-b200: ncclAllReduce failed: %s\n", ncclGetErrorString(r));
+  if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "NCCL-AllReduce [Bytes=%llu]\n", (unsigned long long)(words * sizeof(uint64_t)));
+  if (ranks_out) *ranks_out = ranks;
+  return S;
+}
+}  // namespace hyb
 
 extern "C" void hyacinAllReduce1Drow(const hyacinHandle_t* handle, int32_t Complex, int32_t orderA, uint64_t N, uint64_t* A) {
   if (Complex <= 0 || orderA <= 0 || orderA > 3 || N == 0 || handle->ncclComm == nullptr) return;

@@ -7,6 +7,7 @@
 // thread at a stride of one matrix column; here a 32 x 32 tile goes through shared memory so that both the
 // upper tile and its mirror image are written as contiguous runs.
 #include "hyb_internal.h"
+#include "slices.cuh"
 #include <climits>
 
 namespace hyb {
@@ -99,9 +100,11 @@ template <typename R> struct Elem<R, true> { R re, im; };
 // them to G[y, x] (y fastest) and parks the conjugate in shared memory; phase 2 writes the parked values to
 // G[x, y] (x fastest).  On the diagonal the mirrored value lands last, as it does in the reference
 // (src/fp_i63tp_dequantize.cu:127), so the imaginary part of a diagonal entry is -0.0.
-template <int ORDER, typename R, bool CPLX>
+// SRC: where the integers come from -- the packed limbs (LimbSource) or, after a cross-rank sum, the summed
+// slices (SliceSource): the post-collective epilogue then needs no pass that writes the limbs back.
+template <int ORDER, typename R, bool CPLX, typename SRC>
 __global__ void __launch_bounds__(256)
-dequantize_kernel(int n, const uint64_t* __restrict__ C, const int32_t* __restrict__ vexp, Elem<R, CPLX>* __restrict__ G, int64_t ldg) {
+dequantize_kernel(int n, const SRC src, const int32_t* __restrict__ vexp, Elem<R, CPLX>* __restrict__ G, int64_t ldg) {
   using E = Elem<R, CPLX>;
   __shared__ E tile[32][33];
   // enumerate upper-triangle tile pairs: blockIdx.x -> (by <= bx)
@@ -109,7 +112,6 @@ dequantize_kernel(int n, const uint64_t* __restrict__ C, const int32_t* __restri
   while ((bx + 1) * (bx + 2) / 2 <= int(blockIdx.x)) ++bx;
   while (bx * (bx + 1) / 2 > int(blockIdx.x)) --bx;
   const int by = int(blockIdx.x) - bx * (bx + 1) / 2;
-  const int64_t tri = (int64_t(n) * n + n) / 2;
   const int lx = threadIdx.x, ly = threadIdx.y;
 
   const int y = by * 32 + lx;
@@ -122,14 +124,12 @@ dequantize_kernel(int n, const uint64_t* __restrict__ C, const int32_t* __restri
       E f;
       if (ex == INT_MAX || ey == INT_MAX) { f.re = Conv<R>::zero(); if constexpr (CPLX) f.im = Conv<R>::zero(); }
       else {
-        const uint64_t* src = C + y + (int64_t(x) * (x + 1)) / 2;
+        const uint64_t idx = uint64_t(y) + (uint64_t(x) * (uint64_t(x) + 1)) / 2;
         uint64_t a[ORDER];
-#pragma unroll
-        for (int l = 0; l < ORDER; ++l) a[l] = src[l * tri];
+        src.template load<ORDER>(idx, 0, a);
         f.re = Conv<R>::template run<ORDER>(a, -(ex + ey));
         if constexpr (CPLX) {
-#pragma unroll
-          for (int l = 0; l < ORDER; ++l) a[l] = src[(ORDER + l) * tri];
+          src.template load<ORDER>(idx, 1, a);
           f.im = Conv<R>::template run<ORDER>(a, -(ex + ey));
         }
       }
@@ -148,9 +148,9 @@ dequantize_kernel(int n, const uint64_t* __restrict__ C, const int32_t* __restri
   }
 }
 
-template <int BLOCK, int ORDER>
+template <int BLOCK, int ORDER, typename SRC>
 __global__ void __launch_bounds__(BLOCK)
-gram_range_kernel(int n, const uint64_t* __restrict__ C, int64_t tri, const int32_t* __restrict__ vexp, int32_t* __restrict__ out) {
+gram_range_kernel(int n, const SRC src, const int32_t* __restrict__ vexp, int32_t* __restrict__ out) {
   // key = bit length of the diagonal entry minus twice its column exponent (its true-scale magnitude);
   // the answer is the bit length at the largest key, the longer one on ties.
   __shared__ int s_key[BLOCK / 32], s_len[BLOCK / 32];
@@ -158,10 +158,11 @@ gram_range_kernel(int n, const uint64_t* __restrict__ C, int64_t tri, const int3
   for (int i = threadIdx.x; i < n; i += BLOCK) {
     const int e = vexp[i];
     if (e == INT_MAX) continue;
-    const uint64_t* d = C + (uint64_t(i) * (uint64_t(i) + 3)) / 2;
+    uint64_t d[ORDER];
+    src.template load<ORDER>((uint64_t(i) * (uint64_t(i) + 3)) / 2, 0, d);
     int l = 64 - __clzll((long long)d[0]);
-    if (ORDER > 1) { int ln = 127 - __clzll((long long)d[tri]); l = ln > 63 ? ln : l; }
-    if (ORDER > 2) { int ln = 190 - __clzll((long long)d[2 * tri]); l = ln > 126 ? ln : l; }
+    if (ORDER > 1) { int ln = 127 - __clzll((long long)d[ORDER > 1 ? 1 : 0]); l = ln > 63 ? ln : l; }
+    if (ORDER > 2) { int ln = 190 - __clzll((long long)d[ORDER > 2 ? 2 : 0]); l = ln > 126 ? ln : l; }
     const int k = l - (e + e);
     if (k > key || (k == key && l > len)) { key = k; len = l; }
   }
@@ -178,50 +179,65 @@ gram_range_kernel(int n, const uint64_t* __restrict__ C, int64_t tri, const int3
   }
 }
 
-template <typename R, bool CPLX>
-void run_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, void* G, int64_t ldg) {
+template <typename R, bool CPLX, typename SRC>
+void run_dequantize(cudaStream_t stream, int n, int order, const SRC& src, const int32_t* vexp, void* G, int64_t ldg) {
   const int nb = (n + 31) / 32; const unsigned blocks = unsigned(int64_t(nb) * (nb + 1) / 2);
   dim3 threads(32, 8);
   auto* g = static_cast<Elem<R, CPLX>*>(G);
   switch (order) {
-    case 1: dequantize_kernel<1, R, CPLX><<<blocks, threads, 0, stream>>>(n, C, vexp, g, ldg); break;
-    case 2: dequantize_kernel<2, R, CPLX><<<blocks, threads, 0, stream>>>(n, C, vexp, g, ldg); break;
-    case 3: dequantize_kernel<3, R, CPLX><<<blocks, threads, 0, stream>>>(n, C, vexp, g, ldg); break;
+    case 1: dequantize_kernel<1, R, CPLX, SRC><<<blocks, threads, 0, stream>>>(n, src, vexp, g, ldg); break;
+    case 2: dequantize_kernel<2, R, CPLX, SRC><<<blocks, threads, 0, stream>>>(n, src, vexp, g, ldg); break;
+    case 3: dequantize_kernel<3, R, CPLX, SRC><<<blocks, threads, 0, stream>>>(n, src, vexp, g, ldg); break;
     default: break;
   }
+}
+
+template <typename SRC>
+void range_from(cudaStream_t stream, int n, int order, const SRC& src, const int32_t* vexp, int32_t* bits_out) {
+  count_launch();
+  switch (order) {
+    case 1: gram_range_kernel<512, 1, SRC><<<1, 512, 0, stream>>>(n, src, vexp, bits_out); break;
+    case 2: gram_range_kernel<512, 2, SRC><<<1, 512, 0, stream>>>(n, src, vexp, bits_out); break;
+    case 3: gram_range_kernel<512, 3, SRC><<<1, 512, 0, stream>>>(n, src, vexp, bits_out); break;
+    default: break;
+  }
+  HYB_CUDA(cudaGetLastError());
+}
+
+template <typename SRC>
+void dequantize_from(cudaStream_t stream, int n, int order, const SRC& src, const int32_t* vexp, hyacinPrecision_t gtype, void* G, int64_t ldg) {
+  count_launch();
+  switch (gtype) {
+    case HYACIN_F64: run_dequantize<double, false>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_F32: run_dequantize<float, false>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_DD: run_dequantize<double2, false>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_TF: run_dequantize<float3, false>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_QF: run_dequantize<float4, false>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_F64_COMPLEX: run_dequantize<double, true>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_F32_COMPLEX: run_dequantize<float, true>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_DD_COMPLEX: run_dequantize<double2, true>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_TF_COMPLEX: run_dequantize<float3, true>(stream, n, order, src, vexp, G, ldg); break;
+    case HYACIN_QF_COMPLEX: run_dequantize<float4, true>(stream, n, order, src, vexp, G, ldg); break;
+    default: break;
+  }
+  HYB_CUDA(cudaGetLastError());
 }
 
 }  // namespace
 
 void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, int32_t* bits_out) {
-  const int64_t tri = (int64_t(n) * n + n) / 2;
-  count_launch();
-  switch (order) {
-    case 1: gram_range_kernel<512, 1><<<1, 512, 0, stream>>>(n, C, tri, vexp, bits_out); break;
-    case 2: gram_range_kernel<512, 2><<<1, 512, 0, stream>>>(n, C, tri, vexp, bits_out); break;
-    case 3: gram_range_kernel<512, 3><<<1, 512, 0, stream>>>(n, C, tri, vexp, bits_out); break;
-    default: break;
-  }
-  HYB_CUDA(cudaGetLastError());
+  range_from(stream, n, order, LimbSource{C, (uint64_t(n) * n + n) / 2}, vexp, bits_out);
 }
-
 void launch_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp,
                        hyacinPrecision_t gtype, void* G, int64_t ldg) {
-  count_launch();
-  switch (gtype) {
-    case HYACIN_F64: run_dequantize<double, false>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_F32: run_dequantize<float, false>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_DD: run_dequantize<double2, false>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_TF: run_dequantize<float3, false>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_QF: run_dequantize<float4, false>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_F64_COMPLEX: run_dequantize<double, true>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_F32_COMPLEX: run_dequantize<float, true>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_DD_COMPLEX: run_dequantize<double2, true>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_TF_COMPLEX: run_dequantize<float3, true>(stream, n, order, C, vexp, G, ldg); break;
-    case HYACIN_QF_COMPLEX: run_dequantize<float4, true>(stream, n, order, C, vexp, G, ldg); break;
-    default: break;
-  }
-  HYB_CUDA(cudaGetLastError());
+  dequantize_from(stream, n, order, LimbSource{C, (uint64_t(n) * n + n) / 2}, vexp, gtype, G, ldg);
+}
+void launch_gram_range_slices(cudaStream_t stream, int n, int order, int ranks, const uint64_t* S, const int32_t* vexp, int32_t* bits_out) {
+  range_from(stream, n, order, SliceSource{S, (uint64_t(n) * n + n) / 2, slice_plan(order, ranks)}, vexp, bits_out);
+}
+void launch_dequantize_slices(cudaStream_t stream, int n, int order, int ranks, const uint64_t* S, const int32_t* vexp,
+                              hyacinPrecision_t gtype, void* G, int64_t ldg) {
+  dequantize_from(stream, n, order, SliceSource{S, (uint64_t(n) * n + n) / 2, slice_plan(order, ranks)}, vexp, gtype, G, ldg);
 }
 
 }  // namespace hyb

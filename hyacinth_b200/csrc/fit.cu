@@ -153,11 +153,28 @@ bool build_gram(const hyacinHandle_t* h, double eps, char op, int M, int N, hyac
     hyacinAllReduceVExp(h, uint64_t(N), vexp);
     hyacinXherkBatch(h, batches, seg, lastM, N, type, A, lda, u, vexp, 0, lp, C);
   }
-  hyacinAllReduce1Drow(h, cp, lp, tri, C);
   hyacinPrecision_t gtype = HYACIN_F64;
-  hyacinXdequantizeInit(h, N, lp, C, vexp, type, &gtype, &gbytes);
-  void* G = pool_alloc<char>(h, size_t(N) * N * size_t(gbytes));
-  hyacinXdequantize(h, N, lp, C, vexp, gtype, G, N);
+  void* G = nullptr;
+  int ranks = 1;
+  uint64_t* slices = lp > 0 ? allreduce_to_slices(h, cp, lp, tri, C, &ranks) : nullptr;
+  if (slices) {
+    // Post-collective epilogue in one pass: the summed slices are never written back as limbs; the format scan and
+    // the conversion to floating point re-assemble each integer in registers.
+    timer_mark(h, Segment::Replicated);
+    int32_t* bits_host = static_cast<int32_t*>(h->pinnedWorkspace);
+    *bits_host = 0;
+    launch_gram_range_slices(h->cudaStream, N, lp, ranks, slices, vexp, bits_host);
+    HYB_CUDA(cudaStreamSynchronize(h->cudaStream));
+    gtype = gram_type_from_bits(h, *bits_host, type);
+    gbytes = int(gram_elem_bytes(gtype));
+    G = pool_alloc<char>(h, size_t(N) * N * size_t(gbytes));
+    launch_dequantize_slices(h->cudaStream, N, lp, ranks, slices, vexp, gtype, G, N);
+    pool_free(h, slices);
+  } else {
+    hyacinXdequantizeInit(h, N, lp, C, vexp, type, &gtype, &gbytes);
+    G = pool_alloc<char>(h, size_t(N) * N * size_t(gbytes));
+    hyacinXdequantize(h, N, lp, C, vexp, gtype, G, N);
+  }
   pool_free(h, vexp); pool_free(h, C);
   out->vexp = nullptr; out->C = nullptr; out->G = G; out->gtype = gtype;
   return true;

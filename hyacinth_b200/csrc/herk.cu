@@ -334,6 +334,19 @@ extern "C" void hyacinXherkBatch(const hyacinHandle_t* handle, int32_t batches, 
   hyb::herk_any(handle, rows, N, Atype, A, lda, 'N', u, vexp, beta, orderC, C, batches, segM);
 }
 
+namespace hyb {
+hyacinPrecision_t gram_type_from_bits(const hyacinHandle_t* handle, int raw_bits, hyacinPrecision_t atype) {
+  const int bits = raw_bits - 2 * handle->QuantizeBitCorrection;
+  const bool wide_fp64 = handle->DeviceIsF64Capable != 0;
+  hyacinPrecision_t g = bits <= 23 ? HYACIN_F32_COMPLEX
+                      : bits <= 52 ? HYACIN_F64_COMPLEX
+                      : (bits <= 71 && !wide_fp64) ? HYACIN_TF_COMPLEX
+                      : (bits <= 95 && !wide_fp64) ? HYACIN_QF_COMPLEX : HYACIN_DD_COMPLEX;
+  if (!is_complex(atype)) g = hyacinPrecision_t(int(g) - 1);
+  return g;
+}
+}  // namespace hyb
+
 extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
                                       hyacinPrecision_t Atype, hyacinPrecision_t* Gtype, int32_t* gElemBytes) {
   if (N <= 0 && (Gtype != nullptr || gElemBytes != nullptr)) return;
@@ -345,13 +358,7 @@ extern "C" void hyacinXdequantizeInit(const hyacinHandle_t* handle, int32_t N, i
   HYB_CUDA(cudaStreamSynchronize(handle->cudaStream));
   hyb::status_check(handle, "hyacinXdequantizeInit");
   static const int bytes[12] = {8, 16, 4, 8, 2, 4, 16, 32, 12, 24, 16, 32};
-  const int bits = *bits_host - 2 * handle->QuantizeBitCorrection;
-  const bool wide_fp64 = handle->DeviceIsF64Capable != 0;
-  hyacinPrecision_t g = bits <= 23 ? HYACIN_F32_COMPLEX
-                      : bits <= 52 ? HYACIN_F64_COMPLEX
-                      : (bits <= 71 && !wide_fp64) ? HYACIN_TF_COMPLEX
-                      : (bits <= 95 && !wide_fp64) ? HYACIN_QF_COMPLEX : HYACIN_DD_COMPLEX;
-  if (!hyb::is_complex(Atype)) g = hyacinPrecision_t(int(g) - 1);
+  const hyacinPrecision_t g = hyb::gram_type_from_bits(handle, *bits_host, Atype);
   if (Gtype) *Gtype = g;
   if (gElemBytes) *gElemBytes = bytes[int(g)];
 }
@@ -407,6 +414,26 @@ extern "C" void hyacinB200Reconstruct(const hyacinHandle_t* handle, int32_t N, i
                                       int32_t orderC, uint64_t* Cpanel) {
   if (N <= 0 || moduli <= 0 || moduli > hyb::crt::kMaxModuli || orderC <= 0 || orderC > 3) return;
   hyb::launch_reconstruct(handle->cudaStream, N, moduli, residues, beta ? 1 : 0, orderC, Cpanel);
+}
+
+extern "C" void hyacinB200DequantizeViaSlices(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
+                                             hyacinPrecision_t Atype, int32_t ranks, hyacinPrecision_t* Gtype, void* G, int32_t ldg) {
+  if (N <= 0 || orderC <= 0 || orderC > 3 || ranks < 1 || int(Atype) < 0 || int(Atype) > 11 || !Gtype) return;
+  cudaStream_t stream = handle->cudaStream;
+  const int panels = 1 + hyb::is_complex(Atype);
+  const uint64_t tri = (uint64_t(N) * N + N) / 2;
+  int slices = 0, width = 0; hyb::slice_layout(orderC, ranks, &slices, &width);
+  uint64_t* S = nullptr;
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&S), uint64_t(panels) * slices * tri * sizeof(uint64_t), handle->mempool, stream));
+  if (!S) return;
+  hyb::launch_limbs_to_slices(stream, panels, orderC, ranks, tri, C, S);
+  int32_t* bits_host = static_cast<int32_t*>(handle->pinnedWorkspace);
+  *bits_host = 0;
+  hyb::launch_gram_range_slices(stream, N, orderC, ranks, S, vexp, bits_host);
+  HYB_CUDA(cudaStreamSynchronize(stream));
+  *Gtype = hyb::gram_type_from_bits(handle, *bits_host, Atype);
+  if (G) hyb::launch_dequantize_slices(stream, N, orderC, ranks, S, vexp, *Gtype, G, ldg);
+  HYB_CUDA(cudaFreeAsync(S, stream));
 }
 
 extern "C" void hyacinB200QuantizeLimbs(const hyacinHandle_t* handle, hyacinPrecision_t Atype, int32_t rows, int32_t N, const void* A,

@@ -148,6 +148,18 @@ void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int row
 void launch_reconstruct(cudaStream_t stream, int n, int moduli, const uint8_t* residues, int beta, int order,
                         uint64_t* C_panel, int table = 0);
 
+// The same two steps on the summed slices of a cross-rank reduction (S[panel][slice][tri], layout of slice_plan for
+// `ranks` ranks): the limbs are re-assembled in registers, so the post-collective epilogue needs no pass that writes
+// them back.  Reference counterpart of the fusion: src/allreduce_1drow.cu:112-131 + src/fp_i63tp_dequantize.cu.
+void launch_gram_range_slices(cudaStream_t stream, int n, int order, int ranks, const uint64_t* S, const int32_t* vexp, int32_t* bits_out);
+void launch_dequantize_slices(cudaStream_t stream, int n, int order, int ranks, const uint64_t* S, const int32_t* vexp,
+                              hyacinPrecision_t gtype, void* G, int64_t ldg);
+// Cut C into slices and sum them over the communicator; returns the pool-allocated slice buffer (the caller frees it
+// on the handle's stream) and the communicator size, or nullptr when there is nothing to reduce.
+uint64_t* allreduce_to_slices(const hyacinHandle_t* handle, int panels, int order, uint64_t count, const uint64_t* C, int* ranks_out);
+// Gram format for a given bit length of the largest true-scale diagonal entry (src/fp_i63tp_dequantize.cu:46-54).
+hyacinPrecision_t gram_type_from_bits(const hyacinHandle_t* handle, int bits, hyacinPrecision_t atype);
+
 // Largest bit length among the true-scale diagonal entries (written to *bits_out, device or pinned).
 void launch_gram_range(cudaStream_t stream, int n, int order, const uint64_t* C, const int32_t* vexp, int32_t* bits_out);
 // Packed integer Gram -> full Hermitian floating-point matrix.
@@ -156,6 +168,7 @@ void launch_dequantize(cudaStream_t stream, int n, int order, const uint64_t* C,
 
 // Slices for the cross-rank sum: A[panels][order][count] -> S[panels][slice_count][count] and back.
 int slice_count(int order, int ranks);
+void slice_layout(int order, int ranks, int* slices, int* width);
 void launch_limbs_to_slices(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* A, uint64_t* S);
 void launch_slices_to_limbs(cudaStream_t stream, int panels, int order, int ranks, uint64_t count, const uint64_t* S, uint64_t* A);
 

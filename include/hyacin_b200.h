@@ -85,6 +85,14 @@ int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32_t batches,
  * Takes over the role of the reference's table of limb counts (src/allreduce_1drow.cu:151). */
 void hyacinB200SlicePlan(int32_t orderA, int32_t ranks, int32_t* slices, int32_t* widthBits);
 
+/* Format choice and conversion to floating point straight from the slices of a cross-rank sum: C is cut into the
+ * slices that `ranks` ranks would exchange, and the Gram matrix is produced from those without re-assembling the
+ * limbs in memory (the route the fits take after their all-reduce).  Gives the bits of hyacinXdequantizeInit +
+ * hyacinXdequantize.  Stage counterparts in the reference: src/allreduce_1drow.cu:112-131,
+ * src/fp_i63tp_dequantize.cu:17-26,121-129. */
+void hyacinB200DequantizeViaSlices(const hyacinHandle_t* handle, int32_t N, int32_t orderC, const uint64_t* C, const int32_t* vexp,
+                                   hyacinPrecision_t Atype, int32_t ranks, hyacinPrecision_t* Gtype, void* G, int32_t ldg);
+
 /* Number of kernels this library has launched in the calling process (optionally reset to zero).
  * No counterpart in the reference. */
 int64_t hyacinB200LaunchCount(int32_t reset);

@@ -395,3 +395,28 @@ def test_precision_ladder_over_row_segments_is_exact(hy, atype, spread, zero_blo
     # the plain schedule needs two chunks (quantise + Gram each) and one reconstruction per panel; the ladder adds the
     # segment scan and one reconstruction per run
     assert used >= 8, used
+
+
+@pytest.mark.parametrize("atype,eps,ranks", [(api.F64, 1e-10, 1), (api.F64, 1e-10, 8), (api.F64_COMPLEX, 1e-13, 2),
+                                             (api.F32, 1e-5, 64), (api.F64, 1e-16, 1000)])
+def test_dequantize_from_slices_gives_the_bits_of_the_two_step_route(hy, atype, eps, ranks):
+    """The fits' post-collective route (format scan and conversion straight from the exchanged slices) against
+    hyacinXdequantizeInit + hyacinXdequantize on the limbs: same format, same bits, any communicator size."""
+    torch = _torch()
+    rng = np.random.default_rng(123 + atype + ranks)
+    m, n = 900, 203
+    A = random_matrix(rng, m, n, atype, zero_cols=(11,))
+    dA = to_device_colmajor(A)
+    # size the limbs as a job of `ranks` such row blocks would (the slices must hold the sum over all ranks)
+    u, cp, lp, tri = hy.herk_batch_init(eps, m * ranks, n, atype)
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    C = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
+    gtype, gbytes = hy.dequantize_init(n, lp, C, vexp, atype)
+    ldg = n + 1
+    G1 = torch.zeros((n, ldg * gbytes), dtype=torch.uint8, device="cuda")
+    hy.dequantize(n, lp, C, vexp, gtype, G1, ldg)
+    G2 = torch.zeros_like(G1)
+    g2 = hy.dequantize_via_slices(n, lp, C, vexp, atype, ranks, G2, ldg)
+    torch.cuda.synchronize()
+    assert g2 == gtype
+    assert torch.equal(G1, G2)
