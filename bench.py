@@ -55,6 +55,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-fit", action="store_true", help="skip the hyacinTsvdFit timings (hot path only, e.g. under a profiler)")
+    ap.add_argument("--complex", action="store_true",
+                    help="complex FP64 input (the Gram of BASELINE configuration 4: use --rows-log2 19 --n 2048): hot path only, "
+                         "for profiles of the complex route; not the headline workload")
     return ap.parse_args()
 
 
@@ -129,6 +132,23 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------
 # workload
 # ---------------------------------------------------------------------------------------------------------
+def make_complex_matrix(torch, rows, n, seed):
+    """Column-major rows x n complex FP64 matrix (rank 200, singular values 1 .. 1e-13, noise 1e-15): tensor (n, rows)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(20240611 + 4)
+    r = min(200, n)
+    W, _ = torch.linalg.qr(torch.randn(n, r, dtype=torch.complex128, device="cuda", generator=g))
+    s = 10.0 ** (-13.0 * torch.arange(r, dtype=torch.float64, device="cuda") / max(r - 1, 1))
+    g.manual_seed(seed)
+    At = torch.empty((n, rows), dtype=torch.complex128, device="cuda")
+    blk = 1 << 15
+    for r0 in range(0, rows, blk):
+        k = min(blk, rows - r0)
+        U = torch.randn(k, r, dtype=torch.complex128, device="cuda", generator=g) / (rows ** 0.5)
+        At[:, r0:r0 + k] = ((U * s) @ W.conj().T + 1e-15 * torch.randn(k, n, dtype=torch.complex128, device="cuda", generator=g)).T
+    return At
+
+
 def make_matrix(torch, rows, n, seed):
     """Column-major rows x n FP64 matrix on the device as a tensor of shape (n, rows)."""
     g = torch.Generator(device="cuda")
@@ -191,14 +211,16 @@ def main():
 
     n, rows = args.n, 1 << args.rows_log2
     global_m = rows * world
-    atype = api.F64
-    At = make_matrix(torch, rows, n, seed=777 + rank)
+    if args.complex:
+        args.no_e2e = args.no_cpu = args.no_fit = True
+    atype = api.F64_COMPLEX if args.complex else api.F64
+    At = make_complex_matrix(torch, rows, n, seed=777 + rank) if args.complex else make_matrix(torch, rows, n, seed=777 + rank)
     u, cp, lp, tri = h.herk_batch_init(EPS, global_m, n, atype)
     b, sg, l = h.segments(rows)
     vexp = torch.zeros((b + 1, n), dtype=torch.int32, device="cuda")
     C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
     Gbuf = torch.empty((n, n * 32), dtype=torch.uint8, device="cuda")
-    flops = float(global_m) * n * (n + 1)
+    flops = float(global_m) * n * (n + 1) * (4.0 if args.complex else 1.0)
 
     def barrier():
         torch.cuda.synchronize()
@@ -310,11 +332,12 @@ def main():
         return
 
     out = {
-        "metric": "hyacinTsvdFit FP64-equivalent Gram TFLOP/s (real FP64, 2^%d rows per GPU, N=%d, eps=1e-10)" % (args.rows_log2, n),
+        "metric": "hyacinTsvdFit FP64-equivalent Gram TFLOP/s (%s FP64, 2^%d rows per GPU, N=%d, eps=1e-10)" % ("complex" if args.complex else "real", args.rows_log2, n),
         "value": flops / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s8",
         "data": "synthetic",
-        "config": {"workload": f"hyacinTsvdFit real FP64 opA=N M=2^{args.rows_log2} per GPU N={n} K={n} eps=1e-10 (BASELINE configuration {2 if world == 1 else 3})",
+        "config": {"workload": (f"integer Gram of complex FP64 input, opA=N M=2^{args.rows_log2} per GPU N={n} eps=1e-10 (the Gram of BASELINE configuration 4; hot path only)" if args.complex else
+                                f"hyacinTsvdFit real FP64 opA=N M=2^{args.rows_log2} per GPU N={n} K={n} eps=1e-10 (BASELINE configuration {2 if world == 1 else 3})"),
                    "global_rows": global_m, "quantize_bits": u, "limb_panels": lp, "gram_format": int(gtype),
                    "cache": "inputs (%.1f GiB per GPU) are far larger than the 126 MB L2; no flush needed" % (rows * n * 8 / 2**30)},
         "clocks": clock_info,
@@ -324,7 +347,7 @@ def main():
         "impl": args.impl,
     }
     peaks = json.load(open(PEAKS)) if os.path.exists(PEAKS) else None
-    if mine and prof and prof["gram_launches"]:
+    if mine and prof and prof["gram_launches"] and not args.complex:
         plan = h.crt_plan(u, 0, rows)
         per_launch_rows = min(plan["chunk_rows"], rows)
         alg_ops = 2.0 * plan["moduli"] * per_launch_rows * n * (n + 1) / 2.0          # int8 multiply-adds of the upper triangle, x2
