@@ -19,6 +19,9 @@ NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC,
 ]
+# potrfp.cu must round like the reference's build of the same arithmetic: that build uses --use_fast_math, which
+# for FP32 Gram matrices means flush-to-zero and approximate division / square root (FP64 code is unaffected).
+PER_FILE_FLAGS = {"potrfp.cu": ["--use_fast_math"]}
 LINK_FLAGS = ["-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-Xlinker", "-Bsymbolic",
               "-lcublas", "-lcusolver", "-lnccl"]
 
@@ -42,7 +45,7 @@ def build(force: bool = False, ptxas_verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.join(OBJ, src + ".o")
         if force or _stale(obj, [os.path.join(CSRC, src)] + headers):
-            cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+            cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_verbose else []) + PER_FILE_FLAGS.get(src, []) + ["-c", os.path.join(CSRC, src), "-o", obj]
             jobs.append(cmd)
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:

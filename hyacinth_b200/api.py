@@ -31,7 +31,7 @@ B200_SYMBOLS = [
     "hyacinB200Status", "hyacinB200CrtPlan", "hyacinB200TileInfo", "hyacinB200QuantizeCrt",
     "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
     "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic", "hyacinB200QuantizeLimbs", "hyacinB200GramLimbs",
-    "hyacinB200DequantizeViaSlices",
+    "hyacinB200DequantizeViaSlices", "hyacinB200ProfileReadTail", "hyacinB200PivotedCholesky", "hyacinB200SelfTestWait", "hyacinB200VectorRange",
 ]
 
 
@@ -88,6 +88,10 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200LaunchCount": (i64, [i32]),
         "hyacinB200ProfileEnable": (None, [i32]),
         "hyacinB200ProfileRead": (None, [POINTER(f64), POINTER(i32), POINTER(f64), POINTER(i32)]),
+        "hyacinB200ProfileReadTail": (None, [POINTER(f64), POINTER(i32), POINTER(f64), POINTER(i32)]),
+        "hyacinB200VectorRange": (None, [H, i32, i32, i32, vp, vp]),
+        "hyacinB200SelfTestWait": (i32, [H, c_uint32, c_uint32]),
+        "hyacinB200PivotedCholesky": (i32, [H, f64, i32, i32, i32, vp, i32, vp, vp, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name, None)
@@ -200,6 +204,13 @@ class Hyacin:
     def status(self, clear: bool = True) -> int:
         return int(self.lib.hyacinB200Status(1 if clear else 0))
 
+    def vector_range(self, batches, n, u, vexp, seg_u):
+        self.lib.hyacinB200VectorRange(byref(self.h), batches, n, u, _dp(vexp), _dp(seg_u))
+
+    def self_test_wait(self, poll_limit: int, code: int) -> int:
+        """Make a bounded wait expire on purpose (harmlessly); the code then shows in status()."""
+        return int(self.lib.hyacinB200SelfTestWait(byref(self.h), poll_limit, code))
+
     def launch_count(self, reset: bool = False) -> int:
         return int(self.lib.hyacinB200LaunchCount(1 if reset else 0))
 
@@ -210,6 +221,15 @@ class Hyacin:
         gm, gn, qm, qn = c_double(), c_int32(), c_double(), c_int32()
         self.lib.hyacinB200ProfileRead(byref(gm), byref(gn), byref(qm), byref(qn))
         return {"gram_ms": gm.value, "gram_launches": gn.value, "quantize_ms": qm.value, "quantize_launches": qn.value}
+
+    def profile_read_tail(self):
+        cm, cn, sm, sn = c_double(), c_int32(), c_double(), c_int32()
+        self.lib.hyacinB200ProfileReadTail(byref(cm), byref(cn), byref(sm), byref(sn))
+        return {"cholesky_ms": cm.value, "cholesky_launches": cn.value, "svd_ms": sm.value, "svd_calls": sn.value}
+
+    def pivoted_cholesky(self, eps, n, k, gtype, G, ldg, jpiv, R, ldr) -> int:
+        """Pivoted Cholesky alone: rank, pivots and the factor in pivoted column order (Gram format)."""
+        return int(self.lib.hyacinB200PivotedCholesky(byref(self.h), eps, n, k, gtype, _dp(G), ldg, _dp(jpiv), _dp(R), ldr))
 
     def crt_plan(self, u: int, cplx: int, rows: int):
         a, b, c, d = c_int32(), c_int32(), c_int32(), c_int32()

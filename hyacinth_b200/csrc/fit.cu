@@ -322,24 +322,27 @@ extern "C" int32_t hyacinXGevd(const hyacinHandle_t* handle, double eps, int32_t
   eps = std::min(std::max(std::fabs(eps), machine_eps), 1.);
 
   const size_t gb = gram_elem_bytes(Gtype);
-  const int64_t ldr = factor_row_pitch(N, Gtype);
-  char* Rw = pool_alloc<char>(handle, size_t(N) * ldr * gb);
-  int32_t* jpiv = pool_alloc<int32_t>(handle, N);
-  int rank = potrfp(handle, lrqr ? eps : 0., N, N, Gtype, G, ldg, Rw, ldr, jpiv);
-  pool_free(handle, jpiv);
-  if (rank <= 0) { pool_free(handle, Rw); return 0; }
+  const int64_t ldc = factor_col_pitch(N);
+  char* Rc = pool_alloc<char>(handle, size_t(N) * ldc * gb);
+  int32_t* jpiv = pool_alloc<int32_t>(handle, size_t(2) * N);
+  int32_t* pos = jpiv + N;
+  int rank = potrfp(handle, lrqr ? eps : 0., N, N, Gtype, G, ldg, Rc, ldc, jpiv, pos);
+  if (rank <= 0) { pool_free(handle, jpiv); pool_free(handle, Rc); return 0; }
 
   const size_t lb = gram_elem_bytes(lt), rb = gram_elem_bytes(real_of(lt));
   char* A = pool_alloc<char>(handle, size_t(N) * rank * lb);
-  factor_to_columns(stream, N, rank, Gtype, Rw, ldr, lt, A, N);
-  pool_free(handle, Rw);
+  factor_to_columns(stream, N, rank, Gtype, Rc, ldc, pos, lt, A, N);
+  pool_free(handle, jpiv); pool_free(handle, Rc);
   char* sigma = pool_alloc<char>(handle, size_t(rank) * rb);
   char* U = pool_alloc<char>(handle, size_t(N) * rank * lb);
-  if (sweeps > 0) {
-    char* Vr = pool_alloc<char>(handle, size_t(rank) * rank * lb);
-    gesvdj(handle, lt, N, rank, A, sigma, U, Vr, sweeps, machine_eps);
-    pool_free(handle, Vr);
-  } else gesvd(handle, lt, N, rank, A, sigma, U);
+  {
+    ProfileScope scope(stream, KernelKind::Svd);
+    if (sweeps > 0) {
+      char* Vr = pool_alloc<char>(handle, size_t(rank) * rank * lb);
+      gesvdj(handle, lt, N, rank, A, sigma, U, Vr, sweeps, machine_eps);
+      pool_free(handle, Vr);
+    } else gesvd(handle, lt, N, rank, A, sigma, U);
+  }
   pool_free(handle, A);
   double* suffix = pool_alloc<double>(handle, size_t(std::max(K, rank)));
   int32_t* r_host = static_cast<int32_t*>(handle->pinnedWorkspace);
@@ -369,21 +372,40 @@ extern "C" int32_t hyacinXGinterp(const hyacinHandle_t* handle, double eps, int3
   const double machine_eps = base_type(lt) == HYACIN_F64 ? DBL_EPSILON : double(FLT_EPSILON);
   eps = std::min(std::max(std::fabs(eps), machine_eps), 1.);
   const size_t gb = gram_elem_bytes(Gtype);
-  const int64_t ldr = factor_row_pitch(N, Gtype);
-  char* Rw = pool_alloc<char>(handle, size_t(K) * ldr * gb);
-  const int rank = potrfp(handle, eps, K, N, Gtype, G, ldg, Rw, ldr, jpiv);
+  const int64_t ldc = factor_col_pitch(K);
+  char* Rc = pool_alloc<char>(handle, size_t(N) * ldc * gb);
+  int32_t* pos = pool_alloc<int32_t>(handle, N);
+  const int rank = potrfp(handle, eps, K, N, Gtype, G, ldg, Rc, ldc, jpiv, pos);
+  pool_free(handle, pos);
   if (rank == N) interp_scatter(stream, N, N, jpiv, lt, nullptr, N, Atype, X, ldx);
   else if (rank > 0) {
     const size_t lb = gram_elem_bytes(lt);
     char* B = pool_alloc<char>(handle, size_t(rank) * N * lb);
-    factor_to_pivoted(stream, N, rank, Gtype, Rw, ldr, jpiv, lt, B, rank);
+    factor_to_pivoted(stream, N, rank, Gtype, Rc, ldc, jpiv, lt, B, rank);
     trsm_upper_left(handle, lt, rank, N - rank, B, rank);
     interp_scatter(stream, N, rank, jpiv, lt, B, rank, Atype, X, ldx);
     pool_free(handle, B);
     if (handle->logger) { static const char* names[4] = {"FP64", "FP64-COMPLEX", "FP32", "FP32-COMPLEX"};
       std::fprintf(static_cast<FILE*>(handle->logger), "TRSM-LEFT-%s [M=%d] [N=%d]\n", names[int(lt)], rank, N - rank); }
   }
-  pool_free(handle, Rw);
+  pool_free(handle, Rc);
+  return rank;
+}
+
+// Test hook: the pivoted Cholesky alone.  R comes out as the reference leaves it in the upper triangle of its
+// (overwritten) Gram matrix: R[k + x ldr] = R[k, column jpiv[x] - 1] for k <= x, zero below, in the Gram's format.
+extern "C" int32_t hyacinB200PivotedCholesky(const hyacinHandle_t* handle, double eps, int32_t N, int32_t K, hyacinPrecision_t Gtype, const void* G,
+                                             int32_t ldg, int32_t* jpiv, void* R, int32_t ldr) {
+  const size_t gb = gram_elem_bytes(Gtype);
+  if (N <= 0 || gb == 0) return 0;
+  K = K <= 0 ? N : std::min(N, K);
+  const int64_t ldc = factor_col_pitch(K);
+  char* Rc = pool_alloc<char>(handle, size_t(N) * ldc * gb);
+  int32_t* pos = pool_alloc<int32_t>(handle, N);
+  const int rank = potrfp(handle, eps, K, N, Gtype, G, ldg, Rc, ldc, jpiv, pos);
+  if (rank > 0 && R) factor_copy_pivoted(handle->cudaStream, N, std::min(rank, K), Gtype, Rc, ldc, jpiv, R, ldr);
+  pool_free(handle, pos); pool_free(handle, Rc);
+  HYB_CUDA(cudaStreamSynchronize(handle->cudaStream));
   return rank;
 }
 

@@ -40,6 +40,7 @@ std::atomic<long long> g_launches{0};
 std::atomic<int> g_profile_on{0};
 std::mutex g_profile_mutex;
 std::vector<ProfileEntry> g_profile;
+double g_tail_ms[2] = {0., 0.}; int g_tail_n[2] = {0, 0};      // Cholesky / SVD totals carried between the two read calls
 }  // namespace
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -168,18 +169,38 @@ extern "C" void hyacinB200ProfileEnable(int32_t enable) {
   std::lock_guard<std::mutex> lock(g_profile_mutex);
   for (auto& e : g_profile) { cudaEventDestroy(e.start); cudaEventDestroy(e.stop); }
   g_profile.clear();
+  g_tail_ms[0] = g_tail_ms[1] = 0.; g_tail_n[0] = g_tail_n[1] = 0;
   g_profile_on.store(enable ? 1 : 0);
 }
 
-extern "C" void hyacinB200ProfileRead(double* gramMs, int32_t* gramLaunches, double* quantizeMs, int32_t* quantizeLaunches) {
+namespace {
+void profile_collect(double* ms, int* n) {
   std::lock_guard<std::mutex> lock(g_profile_mutex);
-  double ms[3] = {0., 0., 0.}; int n[3] = {0, 0, 0};
+  for (int i = 0; i < int(KernelKind::Count); ++i) { ms[i] = 0.; n[i] = 0; }
   for (auto& e : g_profile) {
     float t = 0.f;
     if (cudaEventSynchronize(e.stop) == cudaSuccess && cudaEventElapsedTime(&t, e.start, e.stop) == cudaSuccess) { ms[int(e.kind)] += t; n[int(e.kind)] += 1; }
     cudaEventDestroy(e.start); cudaEventDestroy(e.stop);
   }
   g_profile.clear();
+}
+}  // namespace
+
+extern "C" void hyacinB200ProfileRead(double* gramMs, int32_t* gramLaunches, double* quantizeMs, int32_t* quantizeLaunches) {
+  double ms[int(KernelKind::Count)]; int n[int(KernelKind::Count)];
+  profile_collect(ms, n);
   if (gramMs) *gramMs = ms[int(KernelKind::Gram)]; if (gramLaunches) *gramLaunches = n[int(KernelKind::Gram)];
   if (quantizeMs) *quantizeMs = ms[int(KernelKind::Quantize)]; if (quantizeLaunches) *quantizeLaunches = n[int(KernelKind::Quantize)];
+  g_tail_ms[0] += ms[int(KernelKind::Cholesky)]; g_tail_n[0] += n[int(KernelKind::Cholesky)];
+  g_tail_ms[1] += ms[int(KernelKind::Svd)]; g_tail_n[1] += n[int(KernelKind::Svd)];
+}
+
+extern "C" void hyacinB200ProfileReadTail(double* choleskyMs, int32_t* choleskyLaunches, double* svdMs, int32_t* svdCalls) {
+  double ms[int(KernelKind::Count)]; int n[int(KernelKind::Count)];
+  profile_collect(ms, n);
+  g_tail_ms[0] += ms[int(KernelKind::Cholesky)]; g_tail_n[0] += n[int(KernelKind::Cholesky)];
+  g_tail_ms[1] += ms[int(KernelKind::Svd)]; g_tail_n[1] += n[int(KernelKind::Svd)];
+  if (choleskyMs) *choleskyMs = g_tail_ms[0]; if (choleskyLaunches) *choleskyLaunches = g_tail_n[0];
+  if (svdMs) *svdMs = g_tail_ms[1]; if (svdCalls) *svdCalls = g_tail_n[1];
+  g_tail_ms[0] = g_tail_ms[1] = 0.; g_tail_n[0] = g_tail_n[1] = 0;
 }

@@ -383,6 +383,11 @@ extern "C" void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int3
   if (groupRows) *groupRows = p.group_rows; if (chunkRows) *chunkRows = p.chunk_rows;
 }
 
+extern "C" void hyacinB200VectorRange(const hyacinHandle_t* handle, int32_t batches, int32_t N, int32_t u, const int32_t* vexp, int32_t* segU) {
+  if (batches <= 0 || N <= 0) return;
+  hyb::launch_vector_range(handle->cudaStream, batches, N, u, vexp, segU);
+}
+
 extern "C" void hyacinB200TileInfo(int32_t N, int32_t* tileY, int32_t* tileX, int32_t* tilesY, int32_t* numTiles) {
   const hyb::TilePlan tp = hyb::make_tile_plan(N);
   if (tileY) *tileY = hyb::kTileY; if (tileX) *tileX = hyb::kTileX;

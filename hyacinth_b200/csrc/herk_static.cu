@@ -10,21 +10,28 @@
 //
 // The limit.  The array holds kStaticScratchBytes (64 MiB) on every GPU that loads this library, from the
 // moment the module is loaded until the process exits.  A call needs
-//     256 B (status word) + residues: moduli x tiles(N) x 32 KiB (x2 for complex input)
+//     256 B (reserved) + residues: moduli x tiles(N) x 32 KiB (x2 for complex input)
 //                         + one row chunk of int8 planes: chunk x N x moduli (x3 for complex), chunk >= 128
 // and is refused (return value -2, message on stderr) when that does not fit; N up to about 2000 fits for
 // FP64 inputs at eps = 1e-10.  Larger problems must use hyacinXherkBatch.
 //
-// Rules of use.  The first call on a device looks up the device address of the array (cudaGetSymbolAddress);
-// make that first call outside any stream capture.  All calls on a device share the array and it keeps
-// whatever the previous call left in it: everything a call reads is written by that call first (the status word
-// is cleared, padding rows are zero-filled by the quantiser, residues start in overwrite mode), so stale
-// contents never matter -- but two calls whose kernels overlap on the GPU (different streams or handles on the
-// same device) would race on it; issue them on one stream or order them with events.
-// Results are identical to hyacinXherkBatch: only the row chunking differs and the integer Gram is exact.
+// Rules of use.  The first call on a device looks up the device address of the array (cudaGetSymbolAddress),
+// and with CUDA's default lazy module loading that lookup is also what makes the driver load this module and
+// reserve the 64 MiB.  A host whose arena is about to take the rest of the device must therefore make one call
+// BEFORE it does so (or run with CUDA_MODULE_LOADING=EAGER): a call with zero rows is enough, it binds the array
+// and returns 0 without launching anything.  Make that first call outside any stream capture.
+// The handle must come from hyacinCreate on the device that is current at the call (the status word of the
+// bounded waits is set up there); any other combination is refused with -1 / -3 rather than run on the wrong GPU.
+// All calls on a device share the array and it keeps whatever the previous call left in it: everything a call
+// reads is written by that call first (padding rows are zero-filled by the quantiser, residues start in overwrite
+// mode), so stale contents never matter -- but two calls whose kernels overlap on the GPU (different streams or
+// handles on the same device) would race on it; issue them on one stream or order them with events.
+// Complex input always takes the three-part schedule here (planes re, im, -re); handle->GramMatrixAlgorithm is
+// not consulted.  Results are identical to hyacinXherkBatch: only the schedule differs and the integer Gram is exact.
 #include "hyb_internal.h"
 #include <hyacin_b200.h>
 #include <algorithm>
+#include <atomic>
 
 namespace hyb {
 namespace {
@@ -37,21 +44,22 @@ constexpr int kMaxDevices = 64;
 // address a kernel could use; device_scratch() below obtains the real device address.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-unsigned char* g_scratch_addr[kMaxDevices] = {};
+std::atomic<unsigned char*> g_scratch_addr[kMaxDevices];
 
-// Once per device, with that device current.
+// Once per device, with that device current.  Two host threads that make their first call together both look
+// the address up and store the same value.
 unsigned char* device_scratch(int device) {
   if (device < 0 || device >= kMaxDevices) return nullptr;
-  if (!g_scratch_addr[device]) {
-    void* ptr = nullptr;
-    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (err != cudaSuccess || ptr == nullptr) {
-      std::fprintf(stderr, "hyacin-b200: cudaGetSymbolAddress for the static scratch failed: %s\n", cudaGetErrorString(err));
-      return nullptr;
-    }
-    g_scratch_addr[device] = static_cast<unsigned char*>(ptr);
+  unsigned char* known = g_scratch_addr[device].load(std::memory_order_acquire);
+  if (known) return known;
+  void* ptr = nullptr;
+  const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+  if (err != cudaSuccess || ptr == nullptr) {
+    std::fprintf(stderr, "hyacin-b200: cudaGetSymbolAddress for the static scratch failed: %s\n", cudaGetErrorString(err));
+    return nullptr;
   }
-  return g_scratch_addr[device];
+  g_scratch_addr[device].store(static_cast<unsigned char*>(ptr), std::memory_order_release);
+  return static_cast<unsigned char*>(ptr);
 }
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -68,8 +76,23 @@ extern "C" int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32
   const int64_t rows = batches <= 1 ? int64_t(lastM) : int64_t(batches - 1) * segM + lastM;
   const int cplx = is_complex(Atype), parts = cplx ? 3 : 1;
   const int64_t tri = (int64_t(N) * N + N) / 2;
+  // bind the array first, so that a call without rows serves as the warm-up that reserves it
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return -3;
+  if (device != handle->DeviceID) {
+    std::fprintf(stderr, "hyacin-b200: hyacinB200HerkBatchStatic: the handle belongs to device %d but device %d is current\n", handle->DeviceID, device);
+    return -1;
+  }
+  unsigned char* scratch = device_scratch(device);
+  if (!scratch) return -3;
+  // expired waits are reported through the status word that hyacinCreate set up on this device (hyacinB200Status)
+  uint32_t* status = status_word_if_ready(device);
+  if (!status) {
+    std::fprintf(stderr, "hyacin-b200: hyacinB200HerkBatchStatic: no status word on device %d (the handle was not made by hyacinCreate there)\n", device);
+    return -3;
+  }
   if (rows <= 0 || u < 0) {
-    if (beta == 0) HYB_CUDA(cudaMemsetAsync(C, 0, size_t(tri) * orderC * (1 + cplx) * sizeof(uint64_t), stream));
+    if (beta == 0 && C) HYB_CUDA(cudaMemsetAsync(C, 0, size_t(tri) * orderC * (1 + cplx) * sizeof(uint64_t), stream));
     return 0;
   }
   const CrtPlan plan = make_crt_plan(u, cplx, rows, false);
@@ -86,20 +109,7 @@ extern "C" int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32
                  N, plan.moduli, fixed, per_row * kStageK, kStaticScratchBytes);
     return -2;
   }
-  int device = -1;
-  if (cudaGetDevice(&device) != cudaSuccess) return -3;
-  unsigned char* scratch = device_scratch(device);
-  if (!scratch) return -3;
-
   timer_mark(handle, Segment::Distributed);
-  // Expired waits are reported through the handle's usual status word (hyacinB200Status) when hyacinCreate has
-  // already set it up on this device; otherwise through a word at the start of the array, which is the only
-  // part of the scratch that has to start at zero.
-  uint32_t* status = status_word_if_ready(device);
-  if (!status) {
-    status = reinterpret_cast<uint32_t*>(scratch);
-    HYB_CUDA(cudaMemsetAsync(status, 0, kStatusBytes, stream));
-  }
   uint8_t* R = scratch + kStatusBytes;
   int8_t* W = reinterpret_cast<int8_t*>(scratch + fixed);
   const size_t elem = (base_type(Atype) == HYACIN_F64 ? 8 : base_type(Atype) == HYACIN_F32 ? 4 : 2) * size_t(cplx ? 2 : 1);

@@ -24,9 +24,9 @@ uint32_t* status_word_if_ready(int device);      // never allocates: nullptr unt
 uint32_t status_word_read(int device, bool clear);
 void status_check(const hyacinHandle_t* handle, const char* where);
 
-// Launch accounting: every kernel launch of this library is counted; with profiling switched on the Gram and
-// quantise launches are also bracketed by CUDA events on the launching stream (read back by hyacinB200Profile*).
-enum class KernelKind : int { Other = 0, Quantize = 1, Gram = 2 };
+// Launch accounting: every kernel launch of this library is counted; with profiling switched on the Gram,
+// quantise, pivoted-Cholesky and SVD launches are also bracketed by CUDA events on the launching stream (read back by hyacinB200Profile*).
+enum class KernelKind : int { Other = 0, Quantize = 1, Gram = 2, Cholesky = 3, Svd = 4, Count = 5 };
 void count_launch(int n = 1);
 struct ProfileScope {                       // RAII: records start/stop events around one launch when enabled
   ProfileScope(cudaStream_t stream, KernelKind kind);

@@ -33,10 +33,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false if the wait expired or another role already gave up.
+// Bounded wait.  Returns false if the wait expired or another role already gave up.  `limit`: polls before giving
+// up (kSpinLimit everywhere in the product; a self-test passes a small one).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t code) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+                                          uint32_t* status, uint32_t code, uint32_t limit = kSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) { if (*abort_flag) return false; __nanosleep(it > 4096 ? 256 : 32); }
   }

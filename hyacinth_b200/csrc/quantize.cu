@@ -14,6 +14,8 @@
 #include "crt_tables.h"
 #include <cuda_fp16.h>
 #include <climits>
+#include <cstdlib>
+#include <cstring>
 
 namespace hyb {
 namespace {
@@ -23,6 +25,7 @@ struct QuantConsts {
   uint32_t magic[crt::kMaxModuli];          // ceil(2^32 / m)
   uint32_t bias[crt::kMaxModuli];           // (128 - 2^(8 nb - 1)) mod m
   uint32_t weight[crt::kMaxModuli][3];      // 256^b mod m, four per word
+  float inverse[crt::kMaxModuli];           // 1 / m rounded to float (float reduction only)
 };
 
 struct QuantParams {
@@ -150,7 +153,18 @@ __device__ __forceinline__ bool fetch_scaled(const void* A, int64_t lda, const i
   }
 }
 
-template <typename T, int NW, int PARTS, bool TRANS>
+// FR ("float reduction"): the residue sum is reduced on the floating-point pipes instead of the integer one.  The
+// dp4a accumulator starts at the bit pattern of 1.5 * 2^23, so its result, read as a float, IS 1.5 * 2^23 + t
+// exactly (t < 2^20); then q = rint(t / m) by the add-a-big-constant trick and r = t - q m by one fused
+// multiply-add, every intermediate an integer below 2^24 and therefore exact.  1 / m is rounded, so q may differ
+// from the nearest integer when t / m is within 2^20 / 151 * 2^-24 < 5e-4 of a half: |r| <= m / 2 + 5e-4 m < 128,
+// i.e. r is still a representative in [-127, 127], which is all the Gram kernel needs.  The low byte of the
+// result's bit pattern is r in two's complement.  Two dp4a stay on the integer pipe; the four float operations
+// can issue on either floating-point pipe.
+constexpr float kRoundMagic = 12582912.0f;          // 1.5 * 2^23: floats in [2^23, 2^24) have unit spacing
+constexpr uint32_t kRoundMagicBits = 0x4B400000u;
+
+template <typename T, int NW, int PARTS, bool TRANS, bool FR>
 __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
   constexpr int kReal = PARTS == 1 ? 1 : 2;
   int col, row0; double v[kRows][kReal];
@@ -177,12 +191,20 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
         if (NW > 1) t = __dp4a(w[r][1], w1, t);
         if (NW > 2) t = __dp4a(w[r][2], w2, t);
         // modulus 256 (first in the table): the low byte is the residue and the packing below takes only that byte
-        r8[r] = i == 0 ? t : t - __umulhi(t, magic) * modulus;          // exact: t * modulus < 2^32
+        if (i == 0) r8[r] = t;
+        else if constexpr (!FR) r8[r] = t - __umulhi(t, magic) * modulus;          // exact: t * modulus < 2^32
+        else {
+          const float tb = __uint_as_float(t), tf = tb - kRoundMagic;
+          const float qf = fmaf(tf, p.k.inverse[i], kRoundMagic) - kRoundMagic;
+          r8[r] = __float_as_uint(fmaf(-qf, __uint_as_float(modulus), tb));
+        }
       }
-      // four residues per word by byte permutes (ALU pipe), then -128 per byte
+      // four residues per word by byte permutes (ALU pipe); the integer reduction leaves (q + 128) mod m and needs
+      // -128 per byte, the float reduction leaves the centred residue itself
+      const uint32_t flip = (!FR || i == 0) ? 0x80808080u : 0u;
       uint2 packed;
-      packed.x = __byte_perm(__byte_perm(r8[0], r8[1], 0x0040), __byte_perm(r8[2], r8[3], 0x0040), 0x5410) ^ 0x80808080u;
-      packed.y = __byte_perm(__byte_perm(r8[4], r8[5], 0x0040), __byte_perm(r8[6], r8[7], 0x0040), 0x5410) ^ 0x80808080u;
+      packed.x = __byte_perm(__byte_perm(r8[0], r8[1], 0x0040), __byte_perm(r8[2], r8[3], 0x0040), 0x5410) ^ flip;
+      packed.y = __byte_perm(__byte_perm(r8[4], r8[5], 0x0040), __byte_perm(r8[6], r8[7], 0x0040), 0x5410) ^ flip;
       *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch) = packed;
     }
   }
@@ -327,20 +349,42 @@ void launch_limbs_typed(cudaStream_t stream, const LimbParams& p) {
   }
 }
 
-template <typename T, int PARTS>
-void launch_typed(cudaStream_t stream, const QuantParams& p) {
+template <typename T, int PARTS, bool FR>
+void launch_typed_fr(cudaStream_t stream, const QuantParams& p) {
   const int nw = (p.value_bytes + 3) / 4;
   if (p.op == 0) {
     dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
-    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, false><<<grid, 256, 0, stream>>>(p);
-    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, false><<<grid, 256, 0, stream>>>(p);
-    else quantize_crt_kernel<T, 3, PARTS, false><<<grid, 256, 0, stream>>>(p);
+    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, false, FR><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, false, FR><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt_kernel<T, 3, PARTS, false, FR><<<grid, 256, 0, stream>>>(p);
   } else {
     dim3 grid(unsigned(p.ldk / 64), unsigned((p.n + 31) / 32));
-    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, true><<<grid, 256, 0, stream>>>(p);
-    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, true><<<grid, 256, 0, stream>>>(p);
-    else quantize_crt_kernel<T, 3, PARTS, true><<<grid, 256, 0, stream>>>(p);
+    if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, true, FR><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt_kernel<T, 2, PARTS, true, FR><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt_kernel<T, 3, PARTS, true, FR><<<grid, 256, 0, stream>>>(p);
   }
+}
+
+// HYACIN_B200_QUANT_REDUCTION=int selects the integer reduction (multiply-high + multiply-subtract); the default is
+// the float reduction.  Same integer Gram either way.
+bool float_reduction() {
+  static const bool on = [] { const char* v = std::getenv("HYACIN_B200_QUANT_REDUCTION"); return !(v && v[0] == 'i'); }();
+  return on;
+}
+
+template <typename T, int PARTS>
+void launch_typed(cudaStream_t stream, QuantParams& p) {
+  if (float_reduction()) {
+    for (int i = 1; i < crt::kMaxModuli; ++i) {
+      // centred residue of q itself: drop the +128 of the integer scheme, start the sum at the float magic's bits,
+      // and hand the modulus over as a float
+      const uint32_t m = p.k.modulus[i];
+      p.k.bias[i] = kRoundMagicBits + (p.k.bias[i] + m - 128u % m) % m;
+      p.k.inverse[i] = 1.0f / float(m);
+      float mf = float(m); std::memcpy(&p.k.modulus[i], &mf, sizeof(mf));
+    }
+    launch_typed_fr<T, PARTS, true>(stream, p);
+  } else launch_typed_fr<T, PARTS, false>(stream, p);
 }
 
 }  // namespace
@@ -373,7 +417,7 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
   QuantParams p;
   for (int i = 0; i < crt::kMaxModuli; ++i) {   // the bias depends on the byte width of the values
     p.k.modulus[i] = crt::kModulus[i]; p.k.magic[i] = crt::kMagicCeil[i];
-    p.k.bias[i] = crt::kPow2Bias[i][plan.value_bytes - 1];
+    p.k.bias[i] = crt::kPow2Bias[i][plan.value_bytes - 1]; p.k.inverse[i] = 0.f;
     for (int w = 0; w < 3; ++w) p.k.weight[i][w] = crt::kByteWeight[i][w];
   }
   p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;

@@ -7,26 +7,31 @@ namespace hyb {
 size_t gram_elem_bytes(hyacinPrecision_t gtype);
 
 // Truncated pivoted Cholesky.  G: n x n Hermitian Gram in format gtype (F32 / F64 / DD, real or complex), read
-// only.  Rw: cap x n row-major factor in the same format, Rw[k][i] = R[k, original column i] (zero where the
-// column was chosen before step k).  jpiv: n one-based column indices, chosen columns first.  Stops at `cap`
-// rows or when the remaining trace is <= eps^2 * initial trace.  Blocks the host; returns the rank.
+// only.  Rc: the factor in the same format, column-major by ORIGINAL column: Rc[i * ldc + k] = R[k, column i],
+// defined for k <= (position of column i in the pivot order) and k < rank; entries below that diagonal are not
+// written.  ldc = factor_col_pitch(cap) rows per column.  jpiv: n one-based column indices, chosen columns first;
+// pos: its inverse, pos[i] = zero-based position of column i.  Stops at `cap` rows or when the remaining trace is
+// <= eps^2 * initial trace.  Blocks the host; returns the rank.
 int potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, hyacinPrecision_t gtype, const void* G, int64_t ldg,
-           void* Rw, int64_t ldr, int32_t* jpiv);
-// Row pitch (in elements) to allocate Rw with: n rounded up so that a row is a whole number of 16-byte units.
-int64_t factor_row_pitch(int n, hyacinPrecision_t gtype);
+           void* Rc, int64_t ldc, int32_t* jpiv, int32_t* pos);
+// Rows to allocate per column of Rc: cap + 1 rounded up to whole 128-row stages.
+int64_t factor_col_pitch(int cap);
 
 // dst (column-major, ldd) <- op(src) with element conversion.  op: 'N' copy, 'T' transpose, 'C' conjugate
 // transpose.  rows / cols describe dst.  Types are hyacinPrecision_t values 0..5 (F64, F32, F16, real/complex).
 void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecision_t src_type, const void* src, int64_t lds,
                   hyacinPrecision_t dst_type, void* dst, int64_t ldd);
 
-// A (n x rank, column-major, lda) <- R^H with rows in original order: A[i, k] = conj(Rw[k][i]) (0 beyond).
-// dst_type: F64 / F32 (real or complex, matching the Gram).
-void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, hyacinPrecision_t dst_type,
-                       void* A, int64_t lda);
-// B (rank x n, column-major, ldb) <- R in PIVOTED column order: B[k, x] = Rw[k][jpiv[x] - 1], zero below the diagonal.
-void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, const int32_t* jpiv,
+// A (n x rank, column-major, lda) <- R^H with rows in original order: A[i, k] = conj(R[k, column i]) for
+// k <= pos[i], 0 beyond.  dst_type: F64 / F32 (real or complex, matching the Gram).
+void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* pos,
+                       hyacinPrecision_t dst_type, void* A, int64_t lda);
+// B (rank x n, column-major, ldb) <- R in PIVOTED column order: B[k, x] = R[k, column jpiv[x] - 1], zero below the diagonal.
+void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* jpiv,
                        hyacinPrecision_t dst_type, void* B, int64_t ldb);
+// The same in the Gram's own format, bit for bit (what the reference leaves in the upper triangle of G).
+void factor_copy_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* jpiv,
+                         void* B, int64_t ldb);
 // X (n x rank, ldx, type xtype) <- P [I; T^H]: row jpiv[x]-1 gets e_x for x < rank and conj(B[:, x]) otherwise.
 void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, hyacinPrecision_t b_type, const void* B, int64_t ldb,
                     hyacinPrecision_t xtype, void* X, int64_t ldx);

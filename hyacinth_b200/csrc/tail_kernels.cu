@@ -70,29 +70,53 @@ void dispatch_dst(cudaStream_t stream, char op, int rows, int cols, int cplx, co
   }
 }
 
-// A[i + k lda] = conj(Rw[k][i]) -- the factor as an n x rank matrix in original row order.
+// A[i + k lda] = conj(R[k, column i]) for k <= pos[i], else 0 -- the factor as an n x rank matrix in original row
+// order.  The factor is stored with k fastest, A with i fastest: 32 x 32 tiles through shared memory.
 template <typename S, typename D, int CP>
 __global__ void __launch_bounds__(256)
-factor_to_columns_kernel(int n, int rank, const S* __restrict__ Rw, int64_t ldr, D* __restrict__ A, int64_t lda) {
-  const int i = blockIdx.x * 256 + threadIdx.x, k = blockIdx.y;
-  if (i >= n || k >= rank) return;
-  for (int q = 0; q < CP; ++q) {
-    double v = Num<S>::load(Rw + (size_t(k) * ldr + i) * CP + q);
-    Num<D>::store(A + (i + int64_t(k) * lda) * CP + q, q == 1 ? -v : v);
+factor_to_columns_kernel(int n, int rank, const S* __restrict__ Rc, int64_t ldc, const int32_t* __restrict__ pos, D* __restrict__ A, int64_t lda) {
+  __shared__ double tile[CP][32][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int i0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int jj = ty; jj < 32; jj += 8) {
+    const int i = i0 + jj, k = k0 + tx;
+    if (i < n && k < rank) {
+      const bool upper = k <= pos[i];
+      for (int q = 0; q < CP; ++q) {
+        const double v = upper ? Num<S>::load(Rc + (size_t(i) * ldc + k) * CP + q) : 0.;
+        tile[q][jj][tx] = q == 1 ? -v : v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int jj = ty; jj < 32; jj += 8) {
+    const int k = k0 + jj, i = i0 + tx;
+    if (i < n && k < rank)
+      for (int q = 0; q < CP; ++q) Num<D>::store(A + (i + int64_t(k) * lda) * CP + q, tile[q][tx][jj]);
   }
 }
 
-// B[k + x ldb] = Rw[k][jpiv[x] - 1] for k <= x (upper trapezoid in pivoted column order), 0 below the diagonal.
+// B[k + x ldb] = R[k, column jpiv[x] - 1] for k <= x (upper trapezoid in pivoted column order), 0 below the diagonal.
 template <typename S, typename D, int CP>
 __global__ void __launch_bounds__(256)
-factor_to_pivoted_kernel(int n, int rank, const S* __restrict__ Rw, int64_t ldr, const int32_t* __restrict__ jpiv, D* __restrict__ B, int64_t ldb) {
+factor_to_pivoted_kernel(int n, int rank, const S* __restrict__ Rc, int64_t ldc, const int32_t* __restrict__ jpiv, D* __restrict__ B, int64_t ldb) {
   const int k = blockIdx.x * 256 + threadIdx.x, x = blockIdx.y;
   if (k >= rank || x >= n) return;
   const int i = jpiv[x] - 1;
   for (int q = 0; q < CP; ++q) {
-    double v = k <= x ? Num<S>::load(Rw + (size_t(k) * ldr + i) * CP + q) : 0.;
+    double v = k <= x ? Num<S>::load(Rc + (size_t(i) * ldc + k) * CP + q) : 0.;
     Num<D>::store(B + (k + int64_t(x) * ldb) * CP + q, v);
   }
+}
+
+// The same without conversion: 4-byte words of the Gram's own element format.
+__global__ void __launch_bounds__(256)
+factor_copy_pivoted_kernel(int n, int rank, int words, const uint32_t* __restrict__ Rc, int64_t ldc, const int32_t* __restrict__ jpiv,
+                           uint32_t* __restrict__ B, int64_t ldb) {
+  const int k = blockIdx.x * 256 + threadIdx.x, x = blockIdx.y;
+  if (k >= rank || x >= n) return;
+  const int i = jpiv[x] - 1;
+  for (int q = 0; q < words; ++q) B[(k + int64_t(x) * ldb) * words + q] = k <= x ? Rc[(size_t(i) * ldc + k) * words + q] : 0u;
 }
 
 // X[(jpiv[x] - 1) + y ldx] = (x < rank) ? [x == y] : conj(B[y + x ldb]),  y < rank, x < n.
@@ -189,25 +213,25 @@ void convert_copy(cudaStream_t stream, char op, int rows, int cols, hyacinPrecis
   HYB_CUDA(cudaGetLastError());
 }
 
-void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, hyacinPrecision_t dst_type,
-                       void* A, int64_t lda) {
+void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* pos,
+                       hyacinPrecision_t dst_type, void* A, int64_t lda) {
   if (n <= 0 || rank <= 0) return;
   count_launch();
-  dim3 grid((n + 255) / 256, rank);
-#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), ldr, static_cast<D*>(A), lda
+  dim3 grid((n + 31) / 32, (rank + 31) / 32), block(32, 8);
+#define ARGS(S, D) n, rank, static_cast<const S*>(Rc), ldc, pos, static_cast<D*>(A), lda
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
   switch (base_type(gtype)) {
     case HYACIN_F32:
-      if (cplx) { if (to_f64) factor_to_columns_kernel<float, double, 2><<<grid, 256, 0, stream>>>(ARGS(float, double)); else factor_to_columns_kernel<float, float, 2><<<grid, 256, 0, stream>>>(ARGS(float, float)); }
-      else { if (to_f64) factor_to_columns_kernel<float, double, 1><<<grid, 256, 0, stream>>>(ARGS(float, double)); else factor_to_columns_kernel<float, float, 1><<<grid, 256, 0, stream>>>(ARGS(float, float)); }
+      if (cplx) { if (to_f64) factor_to_columns_kernel<float, double, 2><<<grid, block, 0, stream>>>(ARGS(float, double)); else factor_to_columns_kernel<float, float, 2><<<grid, block, 0, stream>>>(ARGS(float, float)); }
+      else { if (to_f64) factor_to_columns_kernel<float, double, 1><<<grid, block, 0, stream>>>(ARGS(float, double)); else factor_to_columns_kernel<float, float, 1><<<grid, block, 0, stream>>>(ARGS(float, float)); }
       break;
     case HYACIN_F64:
-      if (cplx) { if (to_f64) factor_to_columns_kernel<double, double, 2><<<grid, 256, 0, stream>>>(ARGS(double, double)); else factor_to_columns_kernel<double, float, 2><<<grid, 256, 0, stream>>>(ARGS(double, float)); }
-      else { if (to_f64) factor_to_columns_kernel<double, double, 1><<<grid, 256, 0, stream>>>(ARGS(double, double)); else factor_to_columns_kernel<double, float, 1><<<grid, 256, 0, stream>>>(ARGS(double, float)); }
+      if (cplx) { if (to_f64) factor_to_columns_kernel<double, double, 2><<<grid, block, 0, stream>>>(ARGS(double, double)); else factor_to_columns_kernel<double, float, 2><<<grid, block, 0, stream>>>(ARGS(double, float)); }
+      else { if (to_f64) factor_to_columns_kernel<double, double, 1><<<grid, block, 0, stream>>>(ARGS(double, double)); else factor_to_columns_kernel<double, float, 1><<<grid, block, 0, stream>>>(ARGS(double, float)); }
       break;
     case HYACIN_DD:
-      if (cplx) { if (to_f64) factor_to_columns_kernel<DD, double, 2><<<grid, 256, 0, stream>>>(ARGS(DD, double)); else factor_to_columns_kernel<DD, float, 2><<<grid, 256, 0, stream>>>(ARGS(DD, float)); }
-      else { if (to_f64) factor_to_columns_kernel<DD, double, 1><<<grid, 256, 0, stream>>>(ARGS(DD, double)); else factor_to_columns_kernel<DD, float, 1><<<grid, 256, 0, stream>>>(ARGS(DD, float)); }
+      if (cplx) { if (to_f64) factor_to_columns_kernel<DD, double, 2><<<grid, block, 0, stream>>>(ARGS(DD, double)); else factor_to_columns_kernel<DD, float, 2><<<grid, block, 0, stream>>>(ARGS(DD, float)); }
+      else { if (to_f64) factor_to_columns_kernel<DD, double, 1><<<grid, block, 0, stream>>>(ARGS(DD, double)); else factor_to_columns_kernel<DD, float, 1><<<grid, block, 0, stream>>>(ARGS(DD, float)); }
       break;
     default: break;
   }
@@ -215,12 +239,21 @@ void factor_to_columns(cudaStream_t stream, int n, int rank, hyacinPrecision_t g
   HYB_CUDA(cudaGetLastError());
 }
 
-void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rw, int64_t ldr, const int32_t* jpiv,
+void factor_copy_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* jpiv,
+                         void* B, int64_t ldb) {
+  if (n <= 0 || rank <= 0) return;
+  count_launch();
+  factor_copy_pivoted_kernel<<<dim3((rank + 255) / 256, n), 256, 0, stream>>>(n, rank, int(gram_elem_bytes(gtype) / 4), static_cast<const uint32_t*>(Rc), ldc,
+                                                                            jpiv, static_cast<uint32_t*>(B), ldb);
+  HYB_CUDA(cudaGetLastError());
+}
+
+void factor_to_pivoted(cudaStream_t stream, int n, int rank, hyacinPrecision_t gtype, const void* Rc, int64_t ldc, const int32_t* jpiv,
                        hyacinPrecision_t dst_type, void* B, int64_t ldb) {
   if (n <= 0 || rank <= 0) return;
   count_launch();
   dim3 grid((rank + 255) / 256, n);
-#define ARGS(S, D) n, rank, static_cast<const S*>(Rw), ldr, jpiv, static_cast<D*>(B), ldb
+#define ARGS(S, D) n, rank, static_cast<const S*>(Rc), ldc, jpiv, static_cast<D*>(B), ldb
   const int cplx = is_complex(gtype); const bool to_f64 = base_type(dst_type) == HYACIN_F64;
   switch (base_type(gtype)) {
     case HYACIN_F32:

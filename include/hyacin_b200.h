@@ -20,6 +20,13 @@ extern "C" {
  * No counterpart in the reference (its kernels have no waits). */
 uint32_t hyacinB200Status(int32_t clear);
 
+/* Self-test of the bounded waits: runs a one-block kernel that waits, for pollLimit polls (1 .. 65536), on a
+ * barrier that nothing ever completes, so the wait expires the way it would inside the Gram or Cholesky kernels:
+ * the kernel returns, `code` (non-zero) appears in the status word, and the device stays usable.  Returns 0 if
+ * both waiting roles of the kernel reported that they gave up, -1 for bad arguments, -2 otherwise.  Blocks the
+ * host.  No counterpart in the reference. */
+int32_t hyacinB200SelfTestWait(const hyacinHandle_t* handle, uint32_t pollLimit, uint32_t code);
+
 /* Schedule of one hyacinXherkBatch call with `rows` local rows and quantisation bits u: number of CRT
  * moduli, bytes per biased quantised value, rows reconstructed together, rows per kernel launch.
  * Takes over the role of the reference's cost model (src/hyacin_herk.cpp:11-43) for this build.
@@ -28,6 +35,12 @@ uint32_t hyacinB200Status(int32_t clear);
  * that set covers the bit budget, which this query does not report. */
 void hyacinB200CrtPlan(int32_t u, int32_t Complex, int64_t rows, int32_t* moduli, int32_t* valueBytes,
                        int32_t* groupRows, int32_t* chunkRows);
+
+/* Bits each row segment really needs: segU[b] = u + max_j (vexp[0][j] - vexp[b + 1][j]) over the columns that are not
+ * zero in the segment, INT32_MIN for an all-zero segment; vexp is the (batches + 1) x N table of
+ * hyacinXquantizeScaleBatch, segU a device array of `batches` words.  Asynchronous on the handle's stream.
+ * Stage counterpart in the reference: src/fp_exponent.cu:67-76 (internal::int8::vector_range). */
+void hyacinB200VectorRange(const hyacinHandle_t* handle, int32_t batches, int32_t N, int32_t u, const int32_t* vexp, int32_t* segU);
 
 /* Tile geometry of the residue buffers for an N x N Gram: tile height / width, tile rows, and the number of
  * tiles that touch the upper triangle.  A residue buffer holds moduli * numTiles * tileY * tileX bytes. */
@@ -69,11 +82,16 @@ void hyacinB200GramLimbs(const hyacinHandle_t* handle, int32_t N, int32_t order,
  * scratch (int8 residue planes, residue accumulators) lives in a fixed 64 MiB array that is part of the loaded
  * module instead of coming from handle->mempool.  It is meant for hosts that have handed the whole device to
  * their own arena, or that call from a latency-bound loop where an allocator call is not acceptable.
- * Returns 0 on success, -1 for unsupported arguments, -2 (with a message on stderr) when
- * residues(N, moduli) + one 128-row chunk of planes exceed the array -- roughly N > 2000 for FP64 at eps 1e-10 --
- * and -3 if the array's device address could not be obtained.  The first call on a device looks that address
- * up and should be made outside any stream capture.  Calls on one device share the array: keep them on one
- * stream or order them with events; calls whose kernels overlap on the GPU race.
+ * Returns 0 on success; -1 for unsupported arguments or a handle that belongs to another device than the current
+ * one; -2 (with a message on stderr) when residues(N, moduli) + one 128-row chunk of planes exceed the array --
+ * roughly N > 2000 for FP64 at eps 1e-10; -3 if the array's device address or the handle's status word could
+ * not be obtained (the handle must come from hyacinCreate on this device).
+ * The first call on a device looks the array's address up, which with lazy module loading is also the moment the
+ * driver reserves the 64 MiB: make one call -- zero rows is enough, it launches nothing -- before the host takes
+ * the rest of the device memory, and outside any stream capture; from then on the array costs 64 MiB of that
+ * device until the process exits.  Calls on one device share the array: keep them on one stream or order them
+ * with events; calls whose kernels overlap on the GPU race.  Complex input always uses the three-part schedule;
+ * handle->GramMatrixAlgorithm is not consulted.
  * This entry point has no counterpart in the reference, whose hyacinXherkBatch always allocates from the pool. */
 int32_t hyacinB200HerkBatchStatic(const hyacinHandle_t* handle, int32_t batches, int32_t segM, int32_t lastM, int32_t N,
                                   hyacinPrecision_t Atype, const void* A, int32_t lda, int32_t u, const int32_t* vexp,
@@ -97,12 +115,23 @@ void hyacinB200DequantizeViaSlices(const hyacinHandle_t* handle, int32_t N, int3
  * No counterpart in the reference. */
 int64_t hyacinB200LaunchCount(int32_t reset);
 
-/* In-situ kernel timing: while enabled, every quantise and Gram launch is bracketed by CUDA events on its own
- * stream; hyacinB200ProfileRead waits for them, returns total milliseconds and launch counts per kind, and
- * clears the record.  Enabling or disabling also clears it.  No counterpart in the reference (its timer,
- * hyacinSync_TimerSegments, groups work by class, not by kernel). */
+/* In-situ kernel timing: while enabled, every quantise and Gram launch, the pivoted-Cholesky kernel and the
+ * SVD call of hyacinXGevd are bracketed by CUDA events on their own stream; hyacinB200ProfileRead waits for
+ * them, returns total milliseconds and launch counts of the quantise and Gram kernels, and clears the record;
+ * hyacinB200ProfileReadTail does the same for the Cholesky kernel and the SVD call (what either call finds of the
+ * other's kinds is kept for the other).  Enabling or disabling also clears everything.  No counterpart in the
+ * reference (its timer, hyacinSync_TimerSegments, groups work by class, not by kernel). */
 void hyacinB200ProfileEnable(int32_t enable);
 void hyacinB200ProfileRead(double* gramMs, int32_t* gramLaunches, double* quantizeMs, int32_t* quantizeLaunches);
+void hyacinB200ProfileReadTail(double* choleskyMs, int32_t* choleskyLaunches, double* svdMs, int32_t* svdCalls);
+
+/* The truncated pivoted Cholesky of hyacinXGevd / hyacinXGinterp on its own: G (N x N, format Gtype, read only)
+ * -> rank, the one-based pivot order jpiv[N], and the factor R[k + x * ldr] = R(k, column jpiv[x] - 1) for
+ * k <= x, zero below the diagonal, rank rows, in the Gram's own format.  That is the content the reference's
+ * src/hyacin_potrfp.cu:214-272 leaves in the upper triangle of the Gram matrix it overwrites, so the two can be
+ * compared bit for bit.  Blocks the host. */
+int32_t hyacinB200PivotedCholesky(const hyacinHandle_t* handle, double eps, int32_t N, int32_t K, hyacinPrecision_t Gtype,
+                                  const void* G, int32_t ldg, int32_t* jpiv, void* R, int32_t ldr);
 
 #ifdef __cplusplus
 }

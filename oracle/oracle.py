@@ -31,6 +31,11 @@ F64, F64C, F32, F32C, F16, F16C, DD, DDC, TF, TFC, QF, QFC = range(12)
 _NP_OF = {F64: np.float64, F64C: np.complex128, F32: np.float32, F32C: np.complex64, F16: np.float16}
 
 
+def reference_tree() -> str:
+    """Directory of the reference's source tree: $HYACIN_REFERENCE_SRC, else the default of oracle/Makefile."""
+    return subprocess.check_output(["make", "-s", "--no-print-directory", "-C", _HERE, "print-ref"], text=True).strip()
+
+
 def build(force: bool = False) -> str:
     """Compile oracle_gram.c into liboracle.so next to it (gcc, no external dependencies)."""
     so = os.path.join(_HERE, "liboracle.so")

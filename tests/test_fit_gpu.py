@@ -275,29 +275,83 @@ def _synthetic_gram(rng, n, gtype, decades):
     (api.DD_COMPLEX, 1024, 300),
     (api.F32, 5000, 64),            # more column runs than SMs: blocks loop over runs
 ])
-def test_pivoted_cholesky_pivots_identical_to_reference(hy, ref, gtype, n, cap):
-    """hyacinXGinterp on the same Gram matrix: rank, the whole one-based pivot array and the coefficients agree."""
+def test_pivoted_cholesky_factor_bits_identical_to_reference(hy, ref, gtype, n, cap):
+    """The same Gram matrix through both pivoted Choleskys: rank, the whole one-based pivot array and every bit of
+    the factor agree (the reference leaves its factor in the upper triangle of the Gram matrix it overwrites);
+    hyacinXGinterp on top of it then gives identical coefficients."""
     torch = _torch()
     rng = np.random.default_rng(1000 + n + gtype)
     G = _synthetic_gram(rng, n, gtype, {api.F32: 2.0, api.F64: 6.0, api.DD: 12.0}[gtype & ~1])
+    eps = 1e-3 if (gtype & ~1) == api.F32 else 1e-9
+    _compare_cholesky(hy, ref, G, gtype, n, cap, eps)
+
+
+def _compare_cholesky(hy, ref, G, gtype, n, cap, eps):
+    torch = _torch()
     xtype = (api.F32 if (gtype & ~1) == api.F32 else api.F64) | (gtype & 1)
     xdt = {api.F32: torch.float32, api.F64: torch.float64}[xtype & ~1]
     words = 2 if gtype & 1 else 1
-    eps = 1e-3 if (gtype & ~1) == api.F32 else 1e-9
-    out = []
-    for lib in (hy, ref):
-        Gc = G.clone()
-        jp = torch.zeros(n, dtype=torch.int32, device="cuda")
-        X = torch.zeros((cap, n * words), dtype=xdt, device="cuda")        # N x cap, column-major
-        rank = lib.ginterp(eps, n, cap, xtype, X, n, jp, gtype, Gc, n)
-        torch.cuda.synchronize()
-        out.append((rank, jp.cpu().numpy(), X.cpu().numpy().astype(np.float64)))
-    assert out[0][0] == out[1][0] > 0
-    assert np.array_equal(out[0][1], out[1][1]), "pivots differ from the reference"
-    assert sorted(out[0][1].tolist()) == list(range(1, n + 1))
-    scale = max(1.0, np.abs(out[1][2]).max())
-    assert np.max(np.abs(out[0][2] - out[1][2])) <= (1e-2 if (gtype & ~1) == api.F32 else 1e-5) * scale   # triangular solves amplify rounding by the factor's condition
+    gbytes = api.ELEM_BYTES[gtype]
+    # reference: hyacinXGinterp overwrites its Gram matrix; rows < rank of the upper triangle are the factor
+    Gr = G.clone()
+    jp_ref = torch.zeros(n, dtype=torch.int32, device="cuda")
+    X_ref = torch.zeros((cap, n * words), dtype=xdt, device="cuda")        # N x cap, column-major
+    rank_ref = ref.ginterp(eps, n, cap, xtype, X_ref, n, jp_ref, gtype, Gr, n)
+    torch.cuda.synchronize()
+    # this build: the factor through the test hook, the coefficients through hyacinXGinterp
+    Gm = G.clone()
+    jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+    R = torch.zeros((n, cap * gbytes), dtype=torch.uint8, device="cuda")   # cap x N, column-major, Gram format
+    rank = hy.pivoted_cholesky(eps, n, cap, gtype, Gm, n, jp, R, cap)
+    assert torch.equal(Gm.view(torch.uint8), G.view(torch.uint8)), "the Gram matrix must stay untouched"
+    jp2 = torch.zeros(n, dtype=torch.int32, device="cuda")
+    X = torch.zeros((cap, n * words), dtype=xdt, device="cuda")
+    rank2 = hy.ginterp(eps, n, cap, xtype, X, n, jp2, gtype, Gm, n)
+    torch.cuda.synchronize()
+    assert rank == rank2 == rank_ref > 0, (rank, rank2, rank_ref)
+    assert torch.equal(jp, jp_ref) and torch.equal(jp2, jp_ref), "pivots differ from the reference"
+    assert sorted(jp.cpu().tolist()) == list(range(1, n + 1))
+    mine = R.cpu().numpy().reshape(n, cap, gbytes)[:, :rank]                # [x][k][bytes]
+    theirs = Gr.contiguous().view(torch.uint8).cpu().numpy().reshape(n, n, gbytes)[:, :rank]
+    upper = np.arange(rank)[None, :] <= np.arange(n)[:, None]             # k <= x
+    bad = np.argwhere((mine != theirs).any(axis=2) & upper)
+    assert bad.size == 0, f"{len(bad)} factor entries differ from the reference, first at (x, k) = {bad[0].tolist()}"
+    assert not mine[~upper].any(), "entries below the diagonal must be zero"
+    if rank < n:
+        assert torch.equal(X[:rank].view(torch.uint8), X_ref[:rank].view(torch.uint8)), "interpolation coefficients differ"
     assert hy.status() == 0
+    return rank
+
+
+@pytest.mark.parametrize("gtype,n,rho,cap", [(api.F64, 96, 0.5, 96), (api.F64, 300, 0.9, 300), (api.DD, 257, 0.5, 200),
+                                              (api.F32, 200, 0.5, 64), (api.F64_COMPLEX, 130, 0.75, 130)])
+def test_pivoted_cholesky_ties_are_broken_like_the_reference(hy, ref, gtype, n, rho, cap):
+    """G[i, j] = rho^|i - j| has a constant diagonal, and after every step the remaining diagonal is symmetric
+    about the pivots chosen so far, so equal maxima occur at nearly every step: the pivot order then depends only
+    on which of them the reduction meets first."""
+    torch = _torch()
+    idx = np.arange(n)
+    G = rho ** np.abs(idx[:, None] - idx[None, :]).astype(np.float64)
+    base = gtype & ~1
+    if gtype & 1:
+        G = G * np.exp(0.25j * np.pi * (idx[:, None] - idx[None, :]))      # Hermitian, still Toeplitz
+    if base == api.F32:
+        t = torch.from_numpy(np.ascontiguousarray(G.astype(np.complex64 if gtype & 1 else np.float32).T)).cuda()
+    elif base == api.F64:
+        t = torch.from_numpy(np.ascontiguousarray(G.T)).cuda()
+    else:
+        dd = np.zeros((n, n, 2)); dd[:, :, 0] = G.T
+        t = torch.from_numpy(dd).cuda()
+    _compare_cholesky(hy, ref, t, gtype, n, cap, 1e-3 if base == api.F32 else 1e-7)
+
+
+def test_pivoted_cholesky_counts_a_last_single_column(hy, ref):
+    """With K = N the loop stops when one column is left and counts it (src/hyacin_potrfp.cu:264,269 of the
+    reference): a full-rank matrix gives rank N and a complete factor."""
+    rng = np.random.default_rng(3)
+    n = 70
+    G = _synthetic_gram(rng, n, api.F64, 2.0)
+    assert _compare_cholesky(hy, ref, G, api.F64, n, n, 1e-12) == n
 
 
 @pytest.mark.parametrize("op", ["N", "C"])

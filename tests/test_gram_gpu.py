@@ -387,6 +387,12 @@ def test_precision_ladder_over_row_segments_is_exact(hy, atype, spread, zero_blo
     Ao = _oracle_input(A, atype)
     want_vexp = O.column_exponents(Ao, atype, u, *segs)
     np.testing.assert_array_equal(vexp.cpu().numpy(), want_vexp)
+    # bits per row segment, the input of the ladder (reference: src/fp_exponent.cu:67-76)
+    import torch
+    seg_u = torch.zeros(segs[0], dtype=torch.int32, device="cuda")
+    hy.vector_range(segs[0], n, u, vexp, seg_u)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(seg_u.cpu().numpy(), O.vector_range(want_vexp, u))
     hy.launch_count(reset=True)
     C = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
     used = hy.launch_count(reset=True)
@@ -420,3 +426,29 @@ def test_dequantize_from_slices_gives_the_bits_of_the_two_step_route(hy, atype, 
     torch.cuda.synchronize()
     assert g2 == gtype
     assert torch.equal(G1, G2)
+
+
+def test_an_expired_wait_is_reported_and_leaves_the_device_usable(hy):
+    """The bounded waits of the Gram and Cholesky kernels never expire in a healthy run.  The self-test kernel makes
+    one expire harmlessly (a barrier that nothing completes, a short poll limit): the kernel returns, the code shows
+    in the status word, clearing works, and the next real call is still bit-exact."""
+    import torch
+    assert hy.status() == 0
+    assert hy.self_test_wait(2000, 77) == 0
+    assert hy.status(clear=False) == 77
+    assert hy.status(clear=True) == 77
+    assert hy.status() == 0
+    rng = np.random.default_rng(12)
+    m, n, atype, eps = 3000, 200, api.F64, 1e-10
+    A = random_matrix(rng, m, n, atype)
+    dA = to_device_colmajor(A)
+    u, cp, lp, tri = hy.herk_batch_init(eps, m, n, atype)
+    b, s, l = hy.segments(m)
+    vexp = torch.zeros((b + 1, n), dtype=torch.int32, device="cuda")
+    C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
+    hy.quantize_scale_batch(b, s, l, n, atype, dA, m, u, vexp)
+    hy.herk_batch(b, s, l, n, atype, dA, m, u, vexp, 0, lp, C)
+    torch.cuda.synchronize()
+    want_vexp = O.column_exponents(A, atype, u, b, s, l)
+    assert np.array_equal(C.cpu().numpy().view(np.uint64), O.gram_exact(A, atype, want_vexp[0], lp))
+    assert hy.status() == 0

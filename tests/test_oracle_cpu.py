@@ -106,8 +106,9 @@ def test_handle_layout_matches_the_c_header(tmp_path):
     src.write_text(prog)
     want = [ctypes.sizeof(api.HyacinHandle)] + [getattr(api.HyacinHandle, f).offset for f in fields]
     includes = [os.path.join(ROOT, "include")]
-    if os.path.isdir("/root/reference/include"):
-        includes.append("/root/reference/include")
+    ref_include = os.path.join(O.reference_tree(), "include")
+    if os.path.isdir(ref_include):
+        includes.append(ref_include)
     for inc in includes:
         exe = tmp_path / "layout"
         subprocess.check_call(["gcc", "-I", inc, "-I", "/usr/local/cuda/include", str(src), "-o", str(exe)])

@@ -51,3 +51,43 @@ def test_static_scratch_refuses_what_does_not_fit(hy):
     torch.cuda.synchronize()
     assert rc == -2
     assert int((C != 7).sum()) == 0            # refused before touching the output
+
+
+def _pool_attr(pool, attr):
+    """cuMemPoolGetAttribute on the handle's pool: 5 reserved now, 7 used now, 8 used high-water mark."""
+    import ctypes
+    cuda = ctypes.CDLL("libcuda.so.1")
+    val = ctypes.c_uint64(0)
+    assert cuda.cuMemPoolGetAttribute(ctypes.c_void_p(pool), ctypes.c_int(attr), ctypes.byref(val)) == 0
+    return val.value
+
+
+def test_static_scratch_call_allocates_nothing(hy):
+    """A zero-row call binds the module's array and returns 0; after it, a full call leaves the free device memory,
+    the pool's reservation and the pool's high-water mark where they were."""
+    import ctypes
+    import torch
+    n, m, atype, eps = 300, 5000, api.F64, 1e-9
+    rng = np.random.default_rng(11)
+    dA = to_device_colmajor(random_matrix(rng, m, n, atype))
+    u, cp, lp, tri = hy.herk_batch_init(eps, m, n, atype)
+    b, s, l = hy.segments(m)
+    vexp = torch.zeros((b + 1, n), dtype=torch.int32, device="cuda")
+    hy.quantize_scale_batch(b, s, l, n, atype, dA, m, u, vexp)
+    C = torch.zeros((cp * lp, tri), dtype=torch.int64, device="cuda")
+    assert hy.herk_batch_static(1, 0, 0, n, atype, dA, m, u, vexp, 0, lp, C) == 0          # warm-up: no rows
+    assert hy.herk_batch_static(b, s, l, n, atype, dA, m, u, vexp, 0, lp, C) == 0          # loads every kernel once
+    torch.cuda.synchronize()
+    pool = hy.h.mempool
+    cuda = ctypes.CDLL("libcuda.so.1")
+    zero = ctypes.c_uint64(0)
+    assert cuda.cuMemPoolSetAttribute(ctypes.c_void_p(pool), ctypes.c_int(8), ctypes.byref(zero)) == 0   # reset the high-water mark
+    free0, reserved0, used0 = torch.cuda.mem_get_info()[0], _pool_attr(pool, 5), _pool_attr(pool, 7)
+    assert hy.herk_batch_static(b, s, l, n, atype, dA, m, u, vexp, 0, lp, C) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert _pool_attr(pool, 5) == reserved0 and _pool_attr(pool, 7) == used0 and _pool_attr(pool, 8) <= used0
+    want = torch.zeros_like(C)
+    hy.herk_batch(b, s, l, n, atype, dA, m, u, vexp, 0, lp, want)
+    torch.cuda.synchronize()
+    assert torch.equal(C, want) and hy.status() == 0
