@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--n", type=int, default=None)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-peak", action="store_true", help="skip the in-process int8 GEMM peak measurement (e.g. under a profiler)")
+    ap.add_argument("--fits", type=int, default=None, help="number of timed hyacinTsvdFit calls after two warm-up calls (default min(steps, 3); 0 with --fits 0: one call, no warm-up)")
     ap.add_argument("--no-fit", action="store_true", help="skip the hyacinTsvdFit timings (hot path only, e.g. under a profiler)")
     ap.add_argument("--complex", action="store_true",
                     help="complex FP64 input (the Gram of configuration 4: use --rows-log2 19 --n 2048): hot path only, "
@@ -346,7 +348,7 @@ def main():
         h.dequantize(n, lp, C, vexps[0], gtype, Gbuf, n)
         return gtype, gbytes
 
-    int8_peak = int8_gemm_peak(torch, 1.5) if (mine and rank == 0 and not args.complex) else None
+    int8_peak = int8_gemm_peak(torch, 1.5) if (mine and rank == 0 and not args.complex and not args.no_peak) else None
     barrier()
     for _ in range(max(args.warmup, 0)):
         gram_step()
@@ -379,16 +381,18 @@ def main():
     # ---------------- fit with the matrix resident: seconds per hyacinTsvdFit, its timer classes, its tail ----------------
     S = torch.zeros(n, dtype=torch.float64, device="cuda"); V = torch.zeros((n, n), dtype=torch.float64, device="cuda")
     fit_times, seg, fit_rank, tail = [0.0], None, None, None
-    for it in range(0 if args.no_fit else 2 + min(args.steps, 3)):
+    fit_warm = 0 if args.fits == 0 else 2
+    fit_calls = 0 if args.no_fit else (1 if args.fits == 0 else fit_warm + (args.fits if args.fits else min(args.steps, 3)))
+    for it in range(fit_calls):
         h.sync_timer(); barrier()
-        if mine and it == 2:
+        if mine and it == fit_warm:
             h.profile_enable(True)
         t0 = time.perf_counter()
         fit_rank = h.tsvd_fit(eps, "N", rows, n, n, At, rows, S, V, n, global_m, atype)
         seg = h.sync_timer(); torch.cuda.synchronize()
-        if it == 2:
+        if it == fit_warm:
             fit_times = []
-        if it >= 2:
+        if it >= fit_warm:
             fit_times.append(time.perf_counter() - t0)
     fit_seconds = max_over_ranks(statistics.median(fit_times))
     if mine and not args.no_fit:

@@ -80,6 +80,72 @@ def sqrt_minus_one(m):
     raise ValueError(m)
 
 
+# ---- float reduction of the quantiser's residue sums ---------------------------------------------------------
+# The quantiser forms t = bias + sum_b byte_b * weight_b (a non-negative integer below t_max) with dp4a and needs
+# some r = t (mod m) in [-128, 127].  It starts the dp4a accumulator at the BITS of a float X (X = 256 w, 2^23 <= X,
+# X + t_max < 2^24, where floats are the integers), so that the accumulator read as a float is X + t exactly; then
+#     q_m = fmaf(X + t, inv, add)            inv = float(1 / m), add = Y - round(X * inv), Y = 1.5 * 2^23
+# is Y + q with q an integer within 1/2 + slack of t / m (the fused multiply-add rounds once, to unit spacing), and
+#     r   = (X + t) - bits(q_m) * m          (32-bit integer arithmetic, low byte taken)
+# because bits(q_m) = bits(Y) + q and both X and bits(Y) * m are multiples of 256.  w is chosen so that X * inv is as
+# close to an integer as possible, which keeps the slack far below the margin (128 - m / 2) / m; fr_constants()
+# checks every t in [0, t_max) with exact integer arithmetic before a table is emitted.
+FR_Y = 3 << 22
+
+
+def float32_parts(x):
+    """x (a Python float that is exactly a float32) as (mantissa, exponent): x = mantissa * 2^exponent."""
+    import struct
+    bits = struct.unpack("<I", struct.pack("<f", x))[0]
+    e, mant = (bits >> 23) & 0xFF, bits & 0x7FFFFF
+    assert 0 < e < 255
+    return (mant | 0x800000), e - 150, bits
+
+
+def fr_verify(m, X, inv_mant, inv_exp, add, t_max):
+    """Exhaustive check of the float reduction for modulus m; returns the largest |r| seen."""
+    import numpy as np
+    assert inv_exp < 0
+    den = 1 << (-inv_exp)
+    t = np.arange(t_max, dtype=np.int64)
+    tb = X + t
+    assert X % 256 == 0 and X >= (1 << 23) and X + t_max <= (1 << 24)
+    num = tb * inv_mant + add * den                      # exact value of (X + t) * inv + add, times den
+    q_m = num // den
+    rem = num - q_m * den
+    up = (2 * rem > den) | ((2 * rem == den) & (q_m % 2 == 1))      # round to nearest, ties to even
+    q_m = q_m + up
+    assert q_m.min() >= (1 << 23) and q_m.max() < (1 << 24)
+    r = t - (q_m - FR_Y) * m
+    assert r.min() >= -128 and r.max() <= 127 and np.all((r - t) % m == 0)
+    x_bits = 0x4B000000 + (X - (1 << 23))
+    q_bits = 0x4B000000 + (q_m - (1 << 23))
+    low = ((x_bits + t) - q_bits * m) & 0xFF                # what the kernel keeps
+    assert np.all(low == (r & 0xFF))
+    return int(np.abs(r).max())
+
+
+def fr_constants(m, t_max):
+    """(bits of X, bits of inv, bits of add) for modulus m, verified for every t < t_max."""
+    import numpy as np
+    import struct
+    inv = float(np.float32(1.0) / np.float32(m))
+    inv_mant, inv_exp, inv_bits = float32_parts(inv)
+    w = np.arange((1 << 23) // 256, ((1 << 24) - t_max) // 256, dtype=np.int64)
+    den = 1 << (-inv_exp)
+    prod = (w * 256) * inv_mant                          # X * inv, times den
+    frac = prod % den
+    dist = np.minimum(frac, den - frac)
+    best = int(w[int(np.argmin(dist))])
+    X = best * 256
+    z = (X * inv_mant + den // 2) // den                 # round(X * inv)
+    add = FR_Y - z
+    fr_verify(m, X, inv_mant, inv_exp, add, t_max)
+    add_bits = struct.unpack("<I", struct.pack("<f", float(add)))[0]
+    assert struct.unpack("<f", struct.pack("<I", add_bits))[0] == float(add)
+    return 0x4B000000 + (X - (1 << 23)), inv_bits, add_bits
+
+
 def words(v, n):
     return [(v >> (64 * i)) & (2**64 - 1) for i in range(n)]
 
@@ -125,6 +191,16 @@ def emit_set(emit, ns, prefix, mods, complex_set):
     for m in mods:
         rows.append("{ " + ", ".join(str((128 - 2 ** (8 * nb - 1)) % m) for nb in range(1, NBYTES + 1)) + " }")
     emit(f"constexpr uint16_t kPow2Bias[kMaxModuli][{NBYTES}] = {{\n  " + ",\n  ".join(rows) + " };")
+    # residue sums: bias (< m) + 255 * 255 per byte, 12 bytes (24 for the complex set: real and imaginary bytes)
+    t_max = 1 << (21 if complex_set else 20)
+    assert 256 + (2 if complex_set else 1) * NBYTES * 255 * 255 < t_max
+    fr = [fr_constants(m, t_max) if m != 256 else (0, 0, 0) for m in mods]
+    emit("// Float reduction of a residue sum t < 2^%d (see gen_crt_tables.py): the dp4a accumulator starts at kFrBase (the" % (21 if complex_set else 20))
+    emit("// bits of a float X), q_m = fmaf(float(X + t), kFrInv, kFrAdd), and the low byte of (X + t) - bits(q_m) * m is a")
+    emit("// residue of t in [-128, 127].  Float constants are given as bit patterns.  Unused for modulus 256.")
+    emit("constexpr uint32_t kFrBase[kMaxModuli] = { " + ", ".join(f"0x{a:08x}u" for a, _, _ in fr) + " };")
+    emit("constexpr uint32_t kFrInv[kMaxModuli] = { " + ", ".join(f"0x{b:08x}u" for _, b, _ in fr) + " };")
+    emit("constexpr uint32_t kFrAdd[kMaxModuli] = { " + ", ".join(f"0x{c:08x}u" for _, _, c in fr) + " };")
     if complex_set:
         iota = {m: sqrt_minus_one(m) for m in mods}
         emit("// iota_i with iota_i^2 = -1 mod m_i; a complex value maps to p = re - iota im and q = re + iota im.")

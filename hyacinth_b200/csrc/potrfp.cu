@@ -34,13 +34,11 @@
 #include <algorithm>
 #include <cstring>
 
-namespace cg = cooperative_groups;
-
 namespace hyb {
 namespace {
 
 // ---- scalar arithmetic, one policy per Gram format --------------------------------------------------------
-struct DD { double x, y; };
+struct alignas(16) DD { double x, y; };       // 16-byte aligned, like the double2 elements of a double-double Gram matrix
 
 __device__ __forceinline__ DD dd_renorm(double a, double b) { double s = a + b, d = a - s; return DD{s, b + d}; }
 __device__ __forceinline__ DD dd_mul(DD a, DD b) { double p = a.x * b.x; return dd_renorm(p, fma(a.x, b.y, a.y * b.x) + fma(a.x, b.x, -p)); }
@@ -138,9 +136,12 @@ template <typename R, bool CPLX> struct Ops {
 __device__ __forceinline__ float shfl_down_real(float v, int o) { return __shfl_down_sync(0xffffffffu, v, o); }
 __device__ __forceinline__ double shfl_down_real(double v, int o) { return __shfl_down_sync(0xffffffffu, v, o); }
 __device__ __forceinline__ DD shfl_down_real(DD v, int o) { return DD{__shfl_down_sync(0xffffffffu, v.x, o), __shfl_down_sync(0xffffffffu, v.y, o)}; }
+__device__ __forceinline__ float shfl_xor_real(float v, int o) { return __shfl_xor_sync(0xffffffffu, v, o); }
+__device__ __forceinline__ double shfl_xor_real(double v, int o) { return __shfl_xor_sync(0xffffffffu, v, o); }
+__device__ __forceinline__ DD shfl_xor_real(DD v, int o) { return DD{__shfl_xor_sync(0xffffffffu, v.x, o), __shfl_xor_sync(0xffffffffu, v.y, o)}; }
 template <typename R, bool CPLX>
-__device__ __forceinline__ Elem<R, CPLX> shfl_down_elem(Elem<R, CPLX> v, int o) {
-  Elem<R, CPLX> r; r.re = shfl_down_real(v.re, o); if constexpr (CPLX) r.im = shfl_down_real(v.im, o); return r;
+__device__ __forceinline__ Elem<R, CPLX> shfl_xor_elem(Elem<R, CPLX> v, int o) {
+  Elem<R, CPLX> r; r.re = shfl_xor_real(v.re, o); if constexpr (CPLX) r.im = shfl_xor_real(v.im, o); return r;
 }
 
 // ---- block geometry -----------------------------------------------------------------------------------------
@@ -196,9 +197,88 @@ __device__ __forceinline__ int candidate_key(int th, int second) {
   return (((walker * 32 + turn) * 128 + t) << 1) | second;
 }
 
+// ---- one synchronisation per step --------------------------------------------------------------------------
+// At the end of a step every block writes its record for the next one; a cooperative grid barrier follows, and at
+// the top of the next step every block reads ALL records and reduces them in the same order.  Two sets of records
+// alternate by step parity.  (Letting the records themselves be the barrier -- stamped with the step, written with
+// release semantics and polled by every block -- was measured and is slower: 148 x 148 polling reads compete with
+// the writes they wait for.)
+__device__ __forceinline__ float ldcg_real(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ double ldcg_real(const double* p) { return __ldcg(p); }
+// two 8-byte loads: a double-double inside a record is only known to be 8-byte aligned
+__device__ __forceinline__ DD ldcg_real(const DD* p) { return DD{__ldcg(&p->x), __ldcg(&p->y)}; }
+
+template <typename R> __device__ __forceinline__ void publish(Partial<R>* slot, const Partial<R>& p) {
+  slot->val = p.val; slot->trace = p.trace; slot->pos = p.pos; slot->key = p.key; slot->flag = p.flag;
+}
+template <typename R> __device__ __forceinline__ Partial<R> fetch(const Partial<R>* slot) {
+  // L2 loads: these words are rewritten by other blocks every second step
+  Partial<R> p = empty_partial<R>();
+  p.val = ldcg_real(&slot->val); p.trace = __ldcg(&slot->trace); p.pos = __ldcg(&slot->pos); p.key = __ldcg(&slot->key); p.flag = __ldcg(&slot->flag);
+  return p;
+}
+
 struct RingShape { int stages, cw, slot_bytes, strip_off, perm_off, bar_off; };
 
 __device__ __forceinline__ void named_barrier(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+// ---- pieces of a consumer's pass ----------------------------------------------------------------------------
+// The stages of one pass, for a thread that owns chain `chain` of CPG columns starting at tile column c_first.
+template <typename R, bool CPLX, int CPG>
+__device__ __forceinline__ void consume_stages(Elem<R, CPLX>* acc, const uint8_t* ring, const RingShape& shape, uint64_t* full_bar, uint64_t* empty_bar,
+                                               uint32_t& consumed, bool& dead, uint32_t S, int nstages, int k, int chain, int c_first, int lane,
+                                               volatile uint32_t* abort_flag, uint32_t* status) {
+  using E = Elem<R, CPLX>; using O = Ops<R, CPLX>;
+  for (int s = 0; s < nstages; ++s) {
+    const uint32_t slot = consumed % S, round = consumed / S; ++consumed;
+    if (!dead && !ptx::mbar_wait(&full_bar[slot], round & 1u, abort_flag, status, 12u)) dead = true;
+    if (!dead && s * kChains + chain < k) {
+      const uint8_t* base = ring + size_t(slot) * shape.slot_bytes;
+      const E b = reinterpret_cast<const E*>(base + shape.strip_off)[chain];
+      const E* tile = reinterpret_cast<const E*>(base) + size_t(c_first) * kChains + chain;
+#pragma unroll
+      for (int q = 0; q < CPG; ++q) acc[q] = O::chain(acc[q], tile[q * kChains], b);
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+  }
+}
+
+// 32 chains -> one value per column, with the tree of the reference's block reduction: at every level a lane's
+// value is added to that of the lane 1, 2, 4, 8, 16 higher (lower lane first).  While a lane still holds several
+// columns, the two lanes of a pair split them -- each sends the half it gives up and keeps the half it sums -- so
+// the arithmetic is that of the plain tree at a fraction of the additions.  On return lane l < MPG holds the
+// result of column bit_reverse(l).
+template <typename R, bool CPLX, int MPG>
+__device__ __forceinline__ Elem<R, CPLX> tree_reduce(Elem<R, CPLX>* acc, int lane) {
+  using O = Ops<R, CPLX>;
+  int held = MPG;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const bool upper = (lane & o) != 0;
+    if (held > 1) {
+      held >>= 1;
+#pragma unroll
+      for (int q = 0; q < MPG / 2; ++q) {
+        if (q < held) {
+          const Elem<R, CPLX> give = upper ? acc[q] : acc[q + held];
+          const Elem<R, CPLX> got = shfl_xor_elem<R, CPLX>(give, o);
+          acc[q] = upper ? O::add(got, acc[q + held]) : O::add(acc[q], got);
+        }
+      }
+    } else {
+      const Elem<R, CPLX> got = shfl_xor_elem<R, CPLX>(acc[0], o);
+      acc[0] = upper ? O::add(got, acc[0]) : O::add(acc[0], got);
+    }
+  }
+  return acc[0];
+}
+template <int MPG> __device__ __forceinline__ int tree_column_of_lane(int lane) {
+  int c = 0;
+#pragma unroll
+  for (int bit = 1, out = MPG >> 1; out > 0; bit <<= 1, out >>= 1) if (lane & bit) c |= out;
+  return c;
+}
 
 // ---- the kernel ---------------------------------------------------------------------------------------------
 template <typename R, bool CPLX>
@@ -207,23 +287,20 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
                     R* __restrict__ D, int32_t* __restrict__ jpiv, int32_t* __restrict__ pos_out, Partial<R>* __restrict__ partials,
                     int32_t* __restrict__ rank_out, const RingShape shape, uint32_t* __restrict__ status) {
   using E = Elem<R, CPLX>; using O = Ops<R, CPLX>; using T = Real<R>; using P = Partial<R>;
-  cg::grid_group grid = cg::this_grid();
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
   extern __shared__ uint8_t dyn_smem[];
   uint8_t* ring = dyn_smem + ((128u - (ptx::smem_u32(dyn_smem) & 127u)) & 127u);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + shape.bar_off);
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint16_t* perm = reinterpret_cast<uint16_t*>(ring + shape.perm_off);     // position -> original column
   __shared__ E s_part[kGroups][32];                 // tree result of each group of 32 chains, per column of the pass
-  __shared__ P s_red[kThreads / 32];
-  __shared__ P s_best;
+  __shared__ P s_red[2][kThreads / 32];             // by step parity: a warp may still read one step's while another writes the next's
   __shared__ R s_rinv;
-  __shared__ int s_pivot_col;
   __shared__ uint32_t s_abort, s_issued;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblocks = gridDim.x;
   const int cw = shape.cw;
   const uint32_t S = uint32_t(shape.stages);
-  const bool consumer = warp < kConsumerWarps;
   const int grp = warp >> 2, chain = ((warp & 3) << 5) | lane;       // consumers: column group, chain number 0..127
   constexpr uint32_t kColBytes = kChains * sizeof(E);
   constexpr int kMaxPerGroup = PerGroup<E>::value;
@@ -246,12 +323,12 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
       offer(mine, d, i, candidate_key(i, 0));
     }
     warp_merge_partial(mine);
-    if (lane == 0) s_red[warp] = mine;
+    if (lane == 0) s_red[1][warp] = mine;
     __syncthreads();
     if (tid == 0) {
-      P acc = s_red[0];
-      for (int w = 1; w < kThreads / 32; ++w) merge_partial(acc, s_red[w]);
-      partials[blockIdx.x] = acc;
+      P acc = s_red[1][0];
+      for (int w = 1; w < kThreads / 32; ++w) merge_partial(acc, s_red[1][w]);
+      publish(&partials[blockIdx.x], acc);
     }
   }
   grid.sync();
@@ -260,25 +337,18 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
   double threshold = 0.;
   int k = 0, rank = 0;
   for (;; ++k) {
-    // ---- every block reduces the partials of all blocks in the same order: same pivot everywhere ----
+    // ---- read and reduce the records of all blocks in the same order: same pivot everywhere ----
+    P best;
     {
-      const P* cur = partials + size_t(k & 1) * nblocks;
       P mine = empty_partial<R>();
       if (tid < nblocks) {
-        // L2 loads: these words are rewritten by other blocks every second step
-        mine.trace = __ldcg(&cur[tid].trace); mine.pos = __ldcg(&cur[tid].pos); mine.key = __ldcg(&cur[tid].key); mine.flag = __ldcg(&cur[tid].flag);
-        if constexpr (sizeof(R) == 16) { mine.val.x = __ldcg(&cur[tid].val.x); mine.val.y = __ldcg(&cur[tid].val.y); } else mine.val = __ldcg(&cur[tid].val);
+        mine = fetch(&partials[size_t(k & 1) * nblocks + tid]);
       }
-      if (warp * 32 < nblocks) { warp_merge_partial(mine); if (lane == 0) s_red[warp] = mine; }
+      if (warp * 32 < nblocks) { warp_merge_partial(mine); if (lane == 0) s_red[k & 1][warp] = mine; }
       __syncthreads();
-      if (tid == 0) {
-        P acc = s_red[0];
-        for (int w = 1; w * 32 < nblocks; ++w) merge_partial(acc, s_red[w]);
-        s_best = acc;
-      }
-      __syncthreads();
+      best = s_red[k & 1][0];
+      for (int w = 1; w * 32 < nblocks; ++w) merge_partial(best, s_red[k & 1][w]);
     }
-    const P best = s_best;
     const bool have = best.pos >= 0;
     if (best.flag) { rank = -1; break; }
     if (k == 0) {
@@ -297,18 +367,19 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
         break;
       }
     }
+    // The chosen column moves to position k and the column that was there takes its place.  The shared permutation
+    // is updated at the END of the step (the order of columns that are never chosen is part of the result, so the
+    // swap happens only for steps that run); until then everybody reads it through column_at().
     const int q_pivot = best.pos, j = q_pivot - k;   // position of the pivot before the swap, and relative to k
-    // bring the chosen column to position k -- only now that the step is certain to run: the order of the columns
-    // that are never chosen is part of the result
-    if (tid == 0) { const int c = perm[q_pivot]; perm[q_pivot] = perm[k]; perm[k] = uint16_t(c); s_pivot_col = c; }
-    __syncthreads();
-    const int pc = s_pivot_col;
+    const int pc = perm[q_pivot], front = perm[k];
+    auto column_at = [&](int q) -> int { return q == q_pivot ? front : int(perm[q]); };
 
     const int live = n - k - 1;                      // positions k + 1 .. n - 1 after the swap
     const int per_block = (live + nblocks - 1) / nblocks;
     const int lo = k + 1 + blockIdx.x * per_block, hi = min(n, lo + per_block);
     const int nstages = (k + kChains - 1) / kChains;
     const int passes = lo < hi ? (hi - lo + cw - 1) / cw : 0;
+    if (passes == 0) __syncthreads();                // nothing else keeps the warps of this block together before the swap
 
     if (warp == kScalarWarp) {
       if (lane == 0) {
@@ -322,7 +393,7 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
     } else if (warp == kProducerWarp) {
       for (int p = 0; p < passes; ++p) {
         const int r0 = lo + p * cw, cwr = min(cw, hi - r0);
-        const E* src = lane < cwr ? Rc + size_t(perm[r0 + lane]) * ldc : nullptr;
+        const E* src = lane < cwr ? Rc + size_t(column_at(r0 + lane)) * ldc : nullptr;
         const E* strip_src = Rc + size_t(pc) * ldc;
         for (int s = 0; s < nstages; ++s) {
           const uint32_t slot = issued % S, round = issued / S; ++issued;
@@ -344,8 +415,9 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
       P mine = empty_partial<R>();
       for (int p = 0; p < passes; ++p) {
         const int r0 = lo + p * cw, cwr = min(cw, hi - r0);
-        const int cpg = (cwr + kGroups - 1) / kGroups;             // columns per group in this pass
+        const int cpg = (cwr + kGroups - 1) / kGroups;             // columns per group in this pass (the last groups may get fewer)
         const int c_first = grp * cpg;
+        const int my_cols = max(0, min(cpg, cwr - c_first));
         E acc[kMaxPerGroup];
 #pragma unroll
         for (int q = 0; q < kMaxPerGroup; ++q) acc[q] = O::zero();
@@ -353,37 +425,27 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
           // chain 0 starts from the Gram entry (row = this column, column = pivot column)
 #pragma unroll
           for (int q = 0; q < kMaxPerGroup; ++q)
-            if (q < cpg && c_first + q < cwr) acc[q] = G[int64_t(perm[r0 + c_first + q]) + int64_t(pc) * ldg];
+            if (q < my_cols) acc[q] = G[int64_t(column_at(r0 + c_first + q)) + int64_t(pc) * ldg];
         }
         // what the end of the pass needs from global memory is requested now
         R dv = T::zero(); int my_col = 0;
-        if (tid < cwr) { my_col = perm[r0 + tid]; dv = D[my_col]; }
-        for (int s = 0; s < nstages; ++s) {
-          const uint32_t slot = consumed % S, round = consumed / S; ++consumed;
-          if (!dead && !ptx::mbar_wait(&full_bar[slot], round & 1u, &s_abort, status, 12u)) dead = true;
-          if (!dead && s * kChains + chain < k) {
-            const uint8_t* base = ring + size_t(slot) * shape.slot_bytes;
-            const E b = reinterpret_cast<const E*>(base + shape.strip_off)[chain];
-            const E* tile = reinterpret_cast<const E*>(base) + size_t(c_first) * kChains + chain;
-#pragma unroll
-            for (int q = 0; q < kMaxPerGroup; ++q)
-              if (q < cpg && c_first + q < cwr) acc[q] = O::chain(acc[q], tile[q * kChains], b);
-          }
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&empty_bar[slot]);
+        if (tid < cwr) { my_col = column_at(r0 + tid); dv = ldcg_real(&D[my_col]); }
+#define HYB_STAGES(N) case N: consume_stages<R, CPLX, N>(acc, ring, shape, full_bar, empty_bar, consumed, dead, S, nstages, k, chain, c_first, lane, &s_abort, status); break;
+        if constexpr (kMaxPerGroup == 8) {
+          switch (my_cols) { HYB_STAGES(0) HYB_STAGES(1) HYB_STAGES(2) HYB_STAGES(3) HYB_STAGES(4) HYB_STAGES(5) HYB_STAGES(6) HYB_STAGES(7) default: HYB_STAGES(8) }
+        } else {
+          switch (my_cols) { HYB_STAGES(0) HYB_STAGES(1) HYB_STAGES(2) HYB_STAGES(3) default: HYB_STAGES(4) }
         }
+#undef HYB_STAGES
         if (k > 0) {
-          // 32 chains -> one value, partner lanes 1, 2, 4, 8, 16 away; every lane computes, lane 0 holds the tree
-#pragma unroll
-          for (int o = 1; o < 32; o <<= 1)
-#pragma unroll
-            for (int q = 0; q < kMaxPerGroup; ++q)
-              if (q < cpg) acc[q] = O::add(acc[q], shfl_down_elem<R, CPLX>(acc[q], o));
-        }
-        if (lane == 0)
+          const E sum = tree_reduce<R, CPLX, kMaxPerGroup>(acc, lane);
+          const int c = tree_column_of_lane<kMaxPerGroup>(lane);
+          if (lane < kMaxPerGroup && c < my_cols) s_part[warp & 3][c_first + c] = sum;
+        } else if (chain == 0) {
 #pragma unroll
           for (int q = 0; q < kMaxPerGroup; ++q)
-            if (q < cpg && c_first + q < cwr) s_part[warp & 3][c_first + q] = acc[q];
+            if (q < my_cols) s_part[0][c_first + q] = acc[q];
+        }
         named_barrier(1, kConsumers + 32);             // with the scalar warp: s_rinv is ready as well
         if (tid < cwr) {
           E w = s_part[0][tid];
@@ -401,11 +463,15 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
           else key = candidate_key(l - 1, 1);
           offer(mine, dv, r0 + tid, key);
         }
-        named_barrier(2, kConsumers);                  // s_part is rewritten by the next pass
+        if (p + 1 < passes) named_barrier(2, kConsumers);          // s_part is rewritten by the next pass
       }
       if (warp == 0) {
         warp_merge_partial(mine);
-        if (lane == 0) { mine.flag = int(*reinterpret_cast<volatile uint32_t*>(&s_abort)); partials[size_t((k + 1) & 1) * nblocks + blockIdx.x] = mine; }
+        if (lane == 0) {
+          perm[q_pivot] = uint16_t(front); perm[k] = uint16_t(pc);
+          mine.flag = int(*reinterpret_cast<volatile uint32_t*>(&s_abort));
+          publish(&partials[size_t((k + 1) & 1) * nblocks + blockIdx.x], mine);
+        }
       }
     }
     grid.sync();

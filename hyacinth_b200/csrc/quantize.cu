@@ -20,12 +20,19 @@
 namespace hyb {
 namespace {
 
+// HYACIN_B200_QUANT_REDUCTION=int selects the integer reduction of the residue sums (multiply-high + multiply-subtract);
+// the default is the float reduction described at quantize_crt_kernel.  Same integer Gram either way.
+bool float_reduction() {
+  static const bool on = [] { const char* v = std::getenv("HYACIN_B200_QUANT_REDUCTION"); return !(v && v[0] == 'i'); }();
+  return on;
+}
+
 struct QuantConsts {
   uint32_t modulus[crt::kMaxModuli];
   uint32_t magic[crt::kMaxModuli];          // ceil(2^32 / m)
   uint32_t bias[crt::kMaxModuli];           // (128 - 2^(8 nb - 1)) mod m
   uint32_t weight[crt::kMaxModuli][3];      // 256^b mod m, four per word
-  float inverse[crt::kMaxModuli];           // 1 / m rounded to float (float reduction only)
+  uint32_t fr_inv[crt::kMaxModuli], fr_add[crt::kMaxModuli];   // float reduction: bits of float(1 / m) and of the additive constant
 };
 
 struct QuantParams {
@@ -153,17 +160,15 @@ __device__ __forceinline__ bool fetch_scaled(const void* A, int64_t lda, const i
   }
 }
 
-// FR ("float reduction"): the residue sum is reduced on the floating-point pipes instead of the integer one.  The
-// dp4a accumulator starts at the bit pattern of 1.5 * 2^23, so its result, read as a float, IS 1.5 * 2^23 + t
-// exactly (t < 2^20); then q = rint(t / m) by the add-a-big-constant trick and r = t - q m by one fused
-// multiply-add, every intermediate an integer below 2^24 and therefore exact.  1 / m is rounded, so q may differ
-// from the nearest integer when t / m is within 2^20 / 151 * 2^-24 < 5e-4 of a half: |r| <= m / 2 + 5e-4 m < 128,
-// i.e. r is still a representative in [-127, 127], which is all the Gram kernel needs.  The low byte of the
-// result's bit pattern is r in two's complement.  Two dp4a stay on the integer pipe; the four float operations
-// can issue on either floating-point pipe.
-constexpr float kRoundMagic = 12582912.0f;          // 1.5 * 2^23: floats in [2^23, 2^24) have unit spacing
-constexpr uint32_t kRoundMagicBits = 0x4B400000u;
-
+// FR ("float reduction"): the quotient of the residue sum comes from the floating-point pipe instead of an integer
+// multiply-high.  The dp4a accumulator starts at the bit pattern of a float X (>= 2^23, where floats are the
+// integers), so its result read as a float IS X + t exactly; q_m = fmaf(X + t, 1/m, add) is 1.5 * 2^23 + q with q
+// an integer within 1/2 + 6e-4 of t / m (the fused multiply-add rounds once, to unit spacing), and the low byte of
+// (X + t) - bits(q_m) * m, one integer multiply-add, is r = t - q m in two's complement: X and bits(1.5 * 2^23) * m
+// are multiples of 256.  |r| <= 127 for every t the quantiser can form; the constants come from
+// gen_crt_tables.py, which verifies that for each modulus over the whole range of t.  Per residue: two dp4a, one
+// fused multiply-add on either floating-point pipe, one integer multiply-add -- against two dp4a, a multiply-high
+// (two passes of the integer pipe) and an integer multiply-add.
 template <typename T, int NW, int PARTS, bool TRANS, bool FR>
 __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant__ QuantParams p) {
   constexpr int kReal = PARTS == 1 ? 1 : 2;
@@ -193,11 +198,7 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
         // modulus 256 (first in the table): the low byte is the residue and the packing below takes only that byte
         if (i == 0) r8[r] = t;
         else if constexpr (!FR) r8[r] = t - __umulhi(t, magic) * modulus;          // exact: t * modulus < 2^32
-        else {
-          const float tb = __uint_as_float(t), tf = tb - kRoundMagic;
-          const float qf = fmaf(tf, p.k.inverse[i], kRoundMagic) - kRoundMagic;
-          r8[r] = __float_as_uint(fmaf(-qf, __uint_as_float(modulus), tb));
-        }
+        else r8[r] = t - __float_as_uint(fmaf(__uint_as_float(t), __uint_as_float(p.k.fr_inv[i]), __uint_as_float(p.k.fr_add[i]))) * modulus;
       }
       // four residues per word by byte permutes (ALU pipe); the integer reduction leaves (q + 128) mod m and needs
       // -128 per byte, the float reduction leaves the centred residue itself
@@ -221,6 +222,7 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
 struct Quant2mConsts {
   uint32_t modulus[crt2m::kMaxModuli], magic[crt2m::kMaxModuli], bias_p[crt2m::kMaxModuli], bias_q[crt2m::kMaxModuli];
   uint32_t w_re[crt2m::kMaxModuli][3], w_im_p[crt2m::kMaxModuli][3], w_im_q[crt2m::kMaxModuli][3];
+  uint32_t fr_inv[crt2m::kMaxModuli], fr_add[crt2m::kMaxModuli];
 };
 struct Quant2mParams {
   const void* A; int64_t lda; const int32_t* vexp;
@@ -229,7 +231,7 @@ struct Quant2mParams {
   Quant2mConsts k;
 };
 
-template <typename T, int NW, bool TRANS>
+template <typename T, int NW, bool TRANS, bool FR>
 __global__ void __launch_bounds__(256) quantize_crt2m_kernel(const __grid_constant__ Quant2mParams p) {
   int col, row0; double v[kRows][2];
   if (!fetch_scaled<T, 3, TRANS>(p.A, p.lda, p.vexp, p.rows, p.ldk, p.n, p.op, col, row0, v)) return;
@@ -250,32 +252,39 @@ __global__ void __launch_bounds__(256) quantize_crt2m_kernel(const __grid_consta
       uint32_t tp = __dp4a(wi[r][0], p.k.w_im_p[i][0], base + p.k.bias_p[i]), tq = __dp4a(wi[r][0], p.k.w_im_q[i][0], base + p.k.bias_q[i]);
       if (NW > 1) { tp = __dp4a(wi[r][1], p.k.w_im_p[i][1], tp); tq = __dp4a(wi[r][1], p.k.w_im_q[i][1], tq); }
       if (NW > 2) { tp = __dp4a(wi[r][2], p.k.w_im_p[i][2], tp); tq = __dp4a(wi[r][2], p.k.w_im_q[i][2], tq); }
-      rp[r] = tp - __umulhi(tp, magic) * modulus;                       // exact: t < 2^23, t * modulus < 2^32
-      rq[r] = tq - __umulhi(tq, magic) * modulus;
+      if constexpr (!FR) {
+        rp[r] = tp - __umulhi(tp, magic) * modulus;                     // exact: t < 2^23, t * modulus < 2^32
+        rq[r] = tq - __umulhi(tq, magic) * modulus;
+      } else {
+        const float inv = __uint_as_float(p.k.fr_inv[i]), add = __uint_as_float(p.k.fr_add[i]);
+        rp[r] = tp - __float_as_uint(fmaf(__uint_as_float(tp), inv, add)) * modulus;
+        rq[r] = tq - __float_as_uint(fmaf(__uint_as_float(tq), inv, add)) * modulus;
+      }
     }
+    constexpr uint32_t flip = FR ? 0u : 0x80808080u;
     uint2 pp, qq;
-    pp.x = __byte_perm(__byte_perm(rp[0], rp[1], 0x0040), __byte_perm(rp[2], rp[3], 0x0040), 0x5410) ^ 0x80808080u;
-    pp.y = __byte_perm(__byte_perm(rp[4], rp[5], 0x0040), __byte_perm(rp[6], rp[7], 0x0040), 0x5410) ^ 0x80808080u;
-    qq.x = __byte_perm(__byte_perm(rq[0], rq[1], 0x0040), __byte_perm(rq[2], rq[3], 0x0040), 0x5410) ^ 0x80808080u;
-    qq.y = __byte_perm(__byte_perm(rq[4], rq[5], 0x0040), __byte_perm(rq[6], rq[7], 0x0040), 0x5410) ^ 0x80808080u;
+    pp.x = __byte_perm(__byte_perm(rp[0], rp[1], 0x0040), __byte_perm(rp[2], rp[3], 0x0040), 0x5410) ^ flip;
+    pp.y = __byte_perm(__byte_perm(rp[4], rp[5], 0x0040), __byte_perm(rp[6], rp[7], 0x0040), 0x5410) ^ flip;
+    qq.x = __byte_perm(__byte_perm(rq[0], rq[1], 0x0040), __byte_perm(rq[2], rq[3], 0x0040), 0x5410) ^ flip;
+    qq.y = __byte_perm(__byte_perm(rq[4], rq[5], 0x0040), __byte_perm(rq[6], rq[7], 0x0040), 0x5410) ^ flip;
     *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch) = pp;
     *reinterpret_cast<uint2*>(out + int64_t(i) * p.plane_pitch + p.part_pitch) = qq;
   }
 }
 
-template <typename T>
+template <typename T, bool FR>
 void launch_2m_typed(cudaStream_t stream, const Quant2mParams& p) {
   const int nw = (p.value_bytes + 3) / 4;
   if (p.op == 0) {
     dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
-    if (nw <= 1) quantize_crt2m_kernel<T, 1, false><<<grid, 256, 0, stream>>>(p);
-    else if (nw == 2) quantize_crt2m_kernel<T, 2, false><<<grid, 256, 0, stream>>>(p);
-    else quantize_crt2m_kernel<T, 3, false><<<grid, 256, 0, stream>>>(p);
+    if (nw <= 1) quantize_crt2m_kernel<T, 1, false, FR><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt2m_kernel<T, 2, false, FR><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt2m_kernel<T, 3, false, FR><<<grid, 256, 0, stream>>>(p);
   } else {
     dim3 grid(unsigned(p.ldk / 64), unsigned((p.n + 31) / 32));
-    if (nw <= 1) quantize_crt2m_kernel<T, 1, true><<<grid, 256, 0, stream>>>(p);
-    else if (nw == 2) quantize_crt2m_kernel<T, 2, true><<<grid, 256, 0, stream>>>(p);
-    else quantize_crt2m_kernel<T, 3, true><<<grid, 256, 0, stream>>>(p);
+    if (nw <= 1) quantize_crt2m_kernel<T, 1, true, FR><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt2m_kernel<T, 2, true, FR><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt2m_kernel<T, 3, true, FR><<<grid, 256, 0, stream>>>(p);
   }
 }
 
@@ -365,23 +374,14 @@ void launch_typed_fr(cudaStream_t stream, const QuantParams& p) {
   }
 }
 
-// HYACIN_B200_QUANT_REDUCTION=int selects the integer reduction (multiply-high + multiply-subtract); the default is
-// the float reduction.  Same integer Gram either way.
-bool float_reduction() {
-  static const bool on = [] { const char* v = std::getenv("HYACIN_B200_QUANT_REDUCTION"); return !(v && v[0] == 'i'); }();
-  return on;
-}
-
 template <typename T, int PARTS>
 void launch_typed(cudaStream_t stream, QuantParams& p) {
   if (float_reduction()) {
     for (int i = 1; i < crt::kMaxModuli; ++i) {
-      // centred residue of q itself: drop the +128 of the integer scheme, start the sum at the float magic's bits,
-      // and hand the modulus over as a float
+      // residue of q itself (drop the +128 of the integer scheme), summed on top of the bits of the float X
       const uint32_t m = p.k.modulus[i];
-      p.k.bias[i] = kRoundMagicBits + (p.k.bias[i] + m - 128u % m) % m;
-      p.k.inverse[i] = 1.0f / float(m);
-      float mf = float(m); std::memcpy(&p.k.modulus[i], &mf, sizeof(mf));
+      p.k.bias[i] = crt::kFrBase[i] + (p.k.bias[i] + m - 128u % m) % m;
+      p.k.fr_inv[i] = crt::kFrInv[i]; p.k.fr_add[i] = crt::kFrAdd[i];
     }
     launch_typed_fr<T, PARTS, true>(stream, p);
   } else launch_typed_fr<T, PARTS, false>(stream, p);
@@ -395,9 +395,16 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
   if (plan.two_m) {
     if (!cplx || plan.moduli > crt2m::kMaxModuli) return;
     Quant2mParams q;
+    const bool fr = float_reduction();
     for (int i = 0; i < crt2m::kMaxModuli; ++i) {
-      q.k.modulus[i] = crt2m::kModulus[i]; q.k.magic[i] = crt2m::kMagicCeil[i];
+      const uint32_t m = crt2m::kModulus[i];
+      q.k.modulus[i] = m; q.k.magic[i] = crt2m::kMagicCeil[i];
       q.k.bias_p[i] = crt2m::kBiasP[i][plan.value_bytes - 1]; q.k.bias_q[i] = crt2m::kBiasQ[i][plan.value_bytes - 1];
+      q.k.fr_inv[i] = crt2m::kFrInv[i]; q.k.fr_add[i] = crt2m::kFrAdd[i];
+      if (fr) {      // residues of p and q themselves, summed on top of the bits of the float X
+        q.k.bias_p[i] = crt2m::kFrBase[i] + (q.k.bias_p[i] + m - 128u % m) % m;
+        q.k.bias_q[i] = crt2m::kFrBase[i] + (q.k.bias_q[i] + m - 128u % m) % m;
+      }
       for (int w = 0; w < 3; ++w) { q.k.w_re[i][w] = crt2m::kByteWeight[i][w]; q.k.w_im_p[i][w] = crt2m::kByteWeightMinusI[i][w]; q.k.w_im_q[i][w] = crt2m::kByteWeightPlusI[i][w]; }
     }
     q.A = A; q.lda = lda; q.vexp = vexp; q.W = W;
@@ -407,9 +414,9 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
     ProfileScope prof(stream, KernelKind::Quantize);
     count_launch();
     switch (int(atype)) {
-      case HYACIN_F64_COMPLEX: launch_2m_typed<double>(stream, q); break;
-      case HYACIN_F32_COMPLEX: launch_2m_typed<float>(stream, q); break;
-      default: launch_2m_typed<__half>(stream, q); break;
+      case HYACIN_F64_COMPLEX: fr ? launch_2m_typed<double, true>(stream, q) : launch_2m_typed<double, false>(stream, q); break;
+      case HYACIN_F32_COMPLEX: fr ? launch_2m_typed<float, true>(stream, q) : launch_2m_typed<float, false>(stream, q); break;
+      default: fr ? launch_2m_typed<__half, true>(stream, q) : launch_2m_typed<__half, false>(stream, q); break;
     }
     HYB_CUDA(cudaGetLastError());
     return;
@@ -417,7 +424,7 @@ void launch_quantize_crt(cudaStream_t stream, hyacinPrecision_t atype, int rows,
   QuantParams p;
   for (int i = 0; i < crt::kMaxModuli; ++i) {   // the bias depends on the byte width of the values
     p.k.modulus[i] = crt::kModulus[i]; p.k.magic[i] = crt::kMagicCeil[i];
-    p.k.bias[i] = crt::kPow2Bias[i][plan.value_bytes - 1]; p.k.inverse[i] = 0.f;
+    p.k.bias[i] = crt::kPow2Bias[i][plan.value_bytes - 1]; p.k.fr_inv[i] = p.k.fr_add[i] = 0u;
     for (int w = 0; w < 3; ++w) p.k.weight[i][w] = crt::kByteWeight[i][w];
   }
   p.A = A; p.lda = lda; p.vexp = vexp; p.W = W;

@@ -63,3 +63,28 @@ def test_range_bits_of_the_header_match_the_products():
         for m, b in zip(mods, bits):
             prod *= m
             assert 2 ** b < prod <= 2 ** (b + 1)
+
+
+def test_float_reduction_constants_of_the_header_hold_for_every_residue_sum():
+    """The quantiser's float reduction (q = fmaf(X + t, 1 / m, add); residue = low byte of (X + t) - bits(q) m) must
+    give a residue of t in [-128, 127] for EVERY sum t the kernel can form.  Re-checked here from the committed
+    header with exact integer arithmetic, modulus by modulus."""
+    import struct
+    gen = _generator()
+    text = open(os.path.join(CSRC, "crt_tables.h")).read()
+    for ns, t_max in (("crt", 1 << 20), ("crt2m", 1 << 21)):
+        block = text[text.index("namespace " + ns + " {"):]
+        mods = [int(v) for v in re.search(r"kModulus\[kMaxModuli\] = \{([^}]*)\}", block).group(1).split(",")]
+        arr = {name: [int(v.strip().rstrip("u"), 16) for v in re.search(name + r"\[kMaxModuli\] = \{([^}]*)\}", block).group(1).split(",")]
+               for name in ("kFrBase", "kFrInv", "kFrAdd")}
+        # the largest sum: additive constant below m, 255 * 255 per byte, 12 bytes (real and imaginary for the complex set)
+        assert 256 + (2 if ns == "crt2m" else 1) * 12 * 255 * 255 < t_max
+        for i, m in enumerate(mods):
+            if m == 256:
+                continue
+            X = (arr["kFrBase"][i] - 0x4B000000) + (1 << 23)
+            inv = struct.unpack("<f", struct.pack("<I", arr["kFrInv"][i]))[0]
+            add = struct.unpack("<f", struct.pack("<I", arr["kFrAdd"][i]))[0]
+            assert add == int(add)
+            mant, exp, _ = gen.float32_parts(inv)
+            assert gen.fr_verify(m, X, mant, exp, int(add), t_max) <= 127
