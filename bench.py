@@ -79,6 +79,19 @@ class _NcclId(ctypes.Structure):
     _fields_ = [("internal", ctypes.c_byte * 128)]
 
 
+class stdout_to_stderr:
+    """Route file descriptor 1 to stderr for a while: libraries (NCCL's version banner) must not add lines to the JSON output."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *exc):
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def make_nccl_comm(torch, dist, rank, world):
     """ncclComm_t for the handle (the library borrows it, as the reference does)."""
     nccl = ctypes.CDLL("libnccl.so.2")
@@ -246,7 +259,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        with stdout_to_stderr():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
 
     if args.impl == "reference" and not os.path.exists(REF_LIB):
         if rank == 0:
@@ -257,7 +272,8 @@ def main():
     from hyacinth_b200 import api
     comm = None
     if world > 1:
-        nccl, comm = make_nccl_comm(torch, dist, rank, world)
+        with stdout_to_stderr():
+            nccl, comm = make_nccl_comm(torch, dist, rank, world)
     lib_path = REF_LIB if args.impl == "reference" else None
     h = api.Hyacin(lib_path=lib_path, stream=0, nccl_comm=comm.value if comm else None)
     h.h.GramMatrixAlgorithm = args.gram_algorithm.encode()
@@ -375,7 +391,7 @@ def main():
 
     # what the last step computed (outside every timed region)
     check = {"vexp0": checksum(torch, vexps[0][0]), "C": checksum(torch, C), "gram_format": int(gtype),
-             "G": checksum(torch, Gbuf[:, :n * gbytes])}
+             "G": checksum(torch, Gbuf.reshape(-1)[:n * n * gbytes])}       # the N x N Gram (ldg = N) sits at the start of the buffer
     check["ranks_agree"] = ranks_agree((check["C"] or []) + (check["G"] or []))
 
     # ---------------- fit with the matrix resident: seconds per hyacinTsvdFit, its timer classes, its tail ----------------

@@ -56,8 +56,15 @@ struct GramParams {
   // limb mode: planes are the balanced base-256 digits of the quantised values; the accumulator of shift s
   // collects every digit pair (i, j) with i + j = s and is added to the packed integer Gram at bit 8 s
   uint64_t* gram; int64_t tri; int n, order, limb_panels, overwrite;
+  // limb mode with few tiles: one work group per (tile, shift) instead of per tile, so that a small Gram still fills the
+  // GPU; the int32 accumulators go to scratch[tile][shift][kTileY][kTileX] and limb_combine_kernel adds them up
+  int32_t* scratch; int split;
   ModConsts k;
 };
+
+// Shift handled by the r-th group of a tile when the shifts are dealt heaviest first: the middle shift order - 1 collects
+// `order` digit pairs, its neighbours one fewer each.
+__host__ __device__ inline int shift_of_rank(int r, int order) { return (r & 1) ? order - 1 - (r + 1) / 2 : order - 1 + r / 2; }
 
 using namespace ptx;
 
@@ -98,8 +105,9 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
   volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_groups = LIMBS ? p.num_tiles : p.moduli * p.num_tiles;
-  const int subs = LIMBS ? 2 * p.order - 1 : 1;
+  const bool split = LIMBS && p.split != 0;
+  const int num_groups = LIMBS ? (split ? p.num_tiles * (2 * p.order - 1) : p.num_tiles) : p.moduli * p.num_tiles;
+  const int subs = LIMBS ? (split ? 1 : 2 * p.order - 1) : 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
@@ -118,8 +126,9 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
     if (lane == 0) {
       uint32_t stage = 0, phase = 0; bool ok = true;
       for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x) {
-        int ty, tx; tile_of(p, LIMBS ? group : group % p.num_tiles, &ty, &tx);
-        for (int sub = 0; sub < subs && ok; ++sub) {
+        int ty, tx; tile_of(p, group % p.num_tiles, &ty, &tx);
+        for (int step = 0; step < subs && ok; ++step) {
+          const int sub = split ? shift_of_rank(group / p.num_tiles, p.order) : step;
           // plane pairs of this accumulator: (m, m) for residues; (i, sub - i) for limbs
           const int first = LIMBS ? (sub - (p.order - 1) > 0 ? sub - (p.order - 1) : 0) : group / p.num_tiles;
           const int last = LIMBS ? (sub < p.order - 1 ? sub : p.order - 1) : first;
@@ -143,7 +152,8 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
     if (lane == 0) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0; bool ok = true;
       for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x)
-      for (int sub = 0; sub < subs && ok; ++sub) {
+      for (int step = 0; step < subs && ok; ++step) {
+        const int sub = split ? shift_of_rank(group / p.num_tiles, p.order) : step;
         if (!(ok = mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status, 2u))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kTileX;
@@ -173,14 +183,26 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
     const int row = lane_group * 32 + lane;
     uint32_t acc = 0, acc_phase = 0; bool ok = true;
     for (int group = blockIdx.x; group < num_groups && ok; group += gridDim.x)
-    for (int sub = 0; sub < subs && ok; ++sub) {
-      const int m = LIMBS ? 0 : group / p.num_tiles, tile = LIMBS ? group : group % p.num_tiles;
+    for (int step = 0; step < subs && ok; ++step) {
+      const int sub = split ? shift_of_rank(group / p.num_tiles, p.order) : step;
+      const int m = LIMBS ? 0 : group / p.num_tiles, tile = group % p.num_tiles;
       ok = mbar_wait(&bars->acc_full[acc], acc_phase, abort_flag, p.status, 4u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + acc * kTileX;
-      if constexpr (LIMBS) {
+      if (LIMBS && split) {
+        // raw accumulator of this (tile, shift) to scratch: 128 contiguous bytes per thread and load
+        int32_t* out = p.scratch + ((size_t(tile) * (2 * p.order - 1) + sub) * kTileY + row) * size_t(kTileX);
+#pragma unroll 1
+        for (int c = 0; c < kTileX / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) reinterpret_cast<uint4*>(out + c * 32)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+      } else if constexpr (LIMBS) {
         int ty, tx; tile_of(p, tile, &ty, &tx);
         const int y = ty * kTileY + row;
         const bool store_only = p.overwrite && sub == 0;        // first shift of the first chunk of a beta = 0 call
@@ -243,6 +265,25 @@ gram_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ Gr
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Second half of the split limb mode: entry (y, x) of a tile gets sum_s scratch[tile][s][y][x] 2^(8 s) added to its
+// packed 63-bit limbs (or stored, for the first chunk of a beta = 0 call).  One thread per Gram row of the tile, as in
+// the epilogue above, so the limb words of consecutive threads are contiguous.
+__global__ void __launch_bounds__(kTileY) limb_combine_kernel(const GramParams p) {
+  int ty, tx; tile_of(p, blockIdx.x, &ty, &tx);
+  const int y = ty * kTileY + threadIdx.x, shifts = 2 * p.order - 1;
+  if (y >= p.n) return;
+  const int32_t* src = p.scratch + (size_t(blockIdx.x) * shifts * kTileY + threadIdx.x) * size_t(kTileX);
+  for (int q = blockIdx.y * 32; q < blockIdx.y * 32 + 32; ++q) {      // 32 of the tile's columns per block
+    const int x = tx * kTileX + q;
+    if (x >= p.n || y > x) continue;
+    uint64_t* dst = p.gram + y + (int64_t(x) * (x + 1)) / 2;
+    U192 acc192; acc192.w[0] = acc192.w[1] = acc192.w[2] = 0;
+    if (!p.overwrite) acc192 = limbs_to_u192(dst, p.tri, p.limb_panels);
+    for (int sft = 0; sft < shifts; ++sft) add_i32_shifted(acc192, src[size_t(sft) * kTileY * kTileX + q], 8 * sft);
+    store_limbs(acc192, dst, p.tri, p.limb_panels);
+  }
 }
 
 // ---- two-CTA variant (residue Gram over the upper triangle) ---------------------------------------------------
@@ -515,12 +556,24 @@ void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g) {
   p.gram = g.gram; p.tri = (int64_t(g.n) * g.n + g.n) / 2; p.n = g.n; p.order = g.order; p.limb_panels = g.limb_panels;
   p.overwrite = g.overwrite;
   HYB_CUDA(cudaFuncSetAttribute(gram_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
-  int grid = g.sm_count > 0 ? g.sm_count : 148; if (grid > tp.num_tiles) grid = tp.num_tiles;
-  if (grid <= 0 || p.num_kblocks <= 0 || g.order <= 0) return;
+  const int sms = g.sm_count > 0 ? g.sm_count : 148;
+  if (tp.num_tiles <= 0 || p.num_kblocks <= 0 || g.order <= 0) return;
+  // fewer tiles than SMs: deal (tile, shift) pairs to the CTAs instead of tiles and sum the shifts afterwards
+  p.split = (g.scratch != nullptr && tp.num_tiles < sms) ? 1 : 0;
+  p.scratch = g.scratch;
+  const int groups = p.split ? tp.num_tiles * (2 * g.order - 1) : tp.num_tiles;
+  const int grid = groups < sms ? groups : sms;
   ProfileScope prof(stream, KernelKind::Gram);
-  count_launch();
+  count_launch(p.split ? 2 : 1);
   gram_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+  if (p.split) limb_combine_kernel<<<dim3(tp.num_tiles, kTileX / 32), kTileY, 0, stream>>>(p);
   HYB_CUDA(cudaGetLastError());
+}
+
+size_t gram_limbs_scratch_bytes(int n, int order, int sm_count) {
+  const TilePlan tp = make_tile_plan(n);
+  const int sms = sm_count > 0 ? sm_count : 148;
+  return tp.num_tiles < sms ? size_t(tp.num_tiles) * (2 * order - 1) * kTileY * kTileX * sizeof(int32_t) : 0;
 }
 
 }  // namespace hyb

@@ -176,6 +176,9 @@ static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacin
   HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&W), size_t(chunk) * parts * size_t(n) * order, handle->mempool, stream));
   uint32_t* status = status_word_device(handle->DeviceID);
   if (!W || !status) { if (W) cudaFreeAsync(W, stream); return; }
+  int32_t* scratch = nullptr;
+  const size_t scratch_bytes = gram_limbs_scratch_bytes(n, order, handle->DeviceSMs);
+  if (scratch_bytes) HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), scratch_bytes, handle->mempool, stream));
   bool first = true;
   for (int64_t c0 = 0; c0 < rows; c0 += chunk) {
     const int rc = int(std::min<int64_t>(chunk, rows - c0));
@@ -185,12 +188,13 @@ static void herk_limbs(const hyacinHandle_t* handle, int64_t rows, int n, hyacin
     GramLimbLaunch gl{};
     gl.w = W; gl.ldw = ldk * parts; gl.plane_stride = gl.ldw * n; gl.ka0 = 0; gl.kb0 = 0; gl.k_rows = int(ldk) * kmul;
     gl.n = n; gl.order = order; gl.limb_panels = order_c; gl.overwrite = (first && beta == 0) ? 1 : 0;
-    gl.sm_count = handle->DeviceSMs; gl.gram = C; gl.status = status;
+    gl.sm_count = handle->DeviceSMs; gl.gram = C; gl.status = status; gl.scratch = scratch;
     launch_gram_limbs(stream, gl);
     if (cplx) { gl.kb0 = int(ldk); gl.gram = C + size_t(order_c) * tri; launch_gram_limbs(stream, gl); }
     first = false;
   }
   HYB_CUDA(cudaFreeAsync(W, stream));
+  if (scratch) HYB_CUDA(cudaFreeAsync(scratch, stream));
   if (handle->logger) std::fprintf(static_cast<FILE*>(handle->logger), "I8I32-GEMM-%s [algo=TN,limbs,tcgen05] [M=N=%d] [K=%lld] [Order=%d]\n",
                                    cplx ? "COMPLEX" : "REAL", n, (long long)rows, order);
 }

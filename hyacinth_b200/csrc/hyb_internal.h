@@ -135,8 +135,11 @@ struct GramLimbLaunch {
   int ka0, kb0, k_rows, n, order, limb_panels, overwrite, sm_count;
   uint64_t* gram;
   uint32_t* status;
+  int32_t* scratch;             // gram_limbs_scratch_bytes() bytes, or nullptr: with it, a Gram of few tiles is split over (tile, shift)
 };
 void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g);
+// Scratch that lets launch_gram_limbs fill the GPU when the Gram has fewer tiles than the device has SMs (0 otherwise).
+size_t gram_limbs_scratch_bytes(int n, int order, int sm_count);
 // Quantise rows of A into `order` planes of balanced base-256 digits (same plane layout as launch_quantize_crt).
 // Reference counterpart: src/quantize_limbs.cu:29-79.
 void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,
