@@ -205,7 +205,6 @@ __device__ __forceinline__ int candidate_key(int th, int second) {
 // the writes they wait for.)
 __device__ __forceinline__ float ldcg_real(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ double ldcg_real(const double* p) { return __ldcg(p); }
-// two 8-byte loads: a double-double inside a record is only known to be 8-byte aligned
 __device__ __forceinline__ DD ldcg_real(const DD* p) { return DD{__ldcg(&p->x), __ldcg(&p->y)}; }
 
 template <typename R> __device__ __forceinline__ void publish(Partial<R>* slot, const Partial<R>& p) {

@@ -204,6 +204,23 @@ def dequantize(C: np.ndarray, vexp0: np.ndarray, n: int, order: int, gtype: int)
 # Pure-Python big-integer statements (small cases)
 # ------------------------------------------------------------------------------------------------------
 
+def pivoted_cholesky(G: np.ndarray, cap: int, eps: float):
+    """Truncated pivoted Cholesky of an n x n FP64 (real or complex) Gram matrix with the reference's rounding --
+    src/hyacin_potrfp.cu:214-272.  Returns (rank, one-based pivots, R) with R[k, x] = factor entry of row k and the
+    column at pivot position x (zero below the diagonal), `min(cap + 1, n)` rows."""
+    n = G.shape[0]
+    cplx = 1 if np.iscomplexobj(G) else 0
+    Gc = np.asfortranarray(G.astype(np.complex128 if cplx else np.float64))
+    rows = min(cap + 1, n)
+    R = np.zeros((rows, n), dtype=Gc.dtype, order="F")
+    jpiv = np.zeros(n, dtype=np.int32)
+    fn = lib().orc_potrfp_f64
+    fn.restype = ctypes.c_int32
+    rank = fn(ctypes.c_int32(n), ctypes.c_int32(cap), ctypes.c_double(eps), ctypes.c_int32(cplx), _ptr(Gc), ctypes.c_int64(n),
+              _ptr(jpiv), _ptr(R), ctypes.c_int64(rows))
+    return int(rank), jpiv, R
+
+
 def limbs_to_int(words, order: int) -> int:
     """Value of one packed entry given its `order` 63-bit limbs (last limb signed)."""
     v = 0

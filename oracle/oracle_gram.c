@@ -342,3 +342,102 @@ void orc_dequantize(int32_t N, int32_t order, const uint64_t* C, const int32_t* 
     }
   }
 }
+
+/* ---- truncated pivoted Cholesky of a Gram matrix, FP64 real or complex -----------------------------------------
+ * Restates what fixes the BITS of the reference's factor (src/hyacin_potrfp.cu:214-272), sequentially:
+ *   - the new row of a column is  w = G[l, j] - sum_m conj(R[m, l]) R[m, j]  summed as 128 chains (chain t takes the
+ *     previous rows t, t + 128, ... in order with fused multiply-adds, chain 0 starts from the Gram entry; :226-230),
+ *     combined per 32 chains by the tree (x_i + x_{i+1}) + (x_{i+2} + x_{i+3}) ... and then left to right over the four
+ *     groups (the block reduction of :231); the first step has no sum (:223);
+ *   - entry r = w / sqrt(d) as a product with 1 / sqrt(d), diagonal d -= |r|^2 by fused multiply-adds (:172-176);
+ *   - pivot = largest remaining diagonal entry, ties to the candidate the reference's reduction meets first (:243-261);
+ *   - stop when the remaining trace <= eps^2 * initial trace, or N - K columns are left; a single remaining column is
+ *     always counted (:262-269).
+ * Only the double formats are restated: their arithmetic is explicit fused multiply-adds.  The double-double formats
+ * depend on which products the device compiler contracts and are checked against the reference library on the GPU.
+ * G: n x n column-major (2 doubles per entry if cplx).  R: rows x n column-major BY POSITION, R[k + x ldr] for k <= x,
+ * zero elsewhere (what the reference leaves in the upper triangle of its Gram matrix).  jpiv: one-based.  Returns rank. */
+static int chol_key(int th, int second) {
+  int b = th >> 7, t = th & 127, walker = 0, turn = 0;
+  if (b > 0) { walker = (b - 1) & 127; turn = ((b - 1) >> 7) + (walker == 0 ? 1 : 0); }
+  return (((walker * 32 + turn) * 128 + t) << 1) | second;
+}
+static double tree128(const double* x) {
+  double g[4];
+  for (int w = 0; w < 4; ++w) {
+    double v[32];
+    for (int i = 0; i < 32; ++i) v[i] = x[32 * w + i];
+    for (int o = 1; o < 32; o <<= 1) for (int i = 0; i + o < 32; i += 2 * o) v[i] = v[i] + v[i + o];
+    g[w] = v[0];
+  }
+  return ((g[0] + g[1]) + g[2]) + g[3];
+}
+
+int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const double* G, int64_t ldg, int32_t* jpiv, double* R, int64_t ldr) {
+  const int w = cplx ? 2 : 1;
+  if (n <= 0 || cap <= 0) return 0;
+  if (cap > n) cap = n;
+  const int rows = cap + 1 < n ? cap + 1 : n;            /* a counted last column may add one row */
+  double* F = (double*)calloc((size_t)n * rows * w, sizeof(double));      /* F[(col * rows + k) * w]: factor by original column */
+  double* D = (double*)malloc((size_t)n * sizeof(double));
+  int* perm = (int*)malloc((size_t)n * sizeof(int));
+  double re[128], im[128];
+  const double eps_sq = eps * eps;
+  const int iter_n = cap >= n ? 1 : n - cap;
+  /* first candidates: position i is the reference's candidate number i */
+  double trace = 0.0, best = 0.0; int best_pos = -1, best_key = INT_MAX;
+  for (int i = 0; i < n; ++i) {
+    perm[i] = i; D[i] = G[((int64_t)i + (int64_t)i * ldg) * w]; trace += D[i];
+    int key = chol_key(i, 0);
+    if (D[i] > 0.0 && (best_pos < 0 || best < D[i] || (best == D[i] && key < best_key))) { best = D[i]; best_pos = i; best_key = key; }
+  }
+  double threshold = 0.0; int rank = 0, k = 0;
+  for (;; ++k) {
+    const int have = best_pos >= 0;
+    if (k == 0) { if (!have) { rank = 0; break; } threshold = eps_sq * trace; }
+    else {
+      const int remaining = n - k;
+      if (!(have && threshold < trace) || remaining <= iter_n) {
+        rank = k + (remaining == 1 ? 1 : 0);
+        if (remaining == 1) F[((size_t)perm[k] * rows + k) * w] = sqrt(have ? best : 0.0);
+        break;
+      }
+    }
+    const int q = best_pos, j = q - k, pc = perm[q], front = perm[k];
+    const double root = sqrt(best), rinv = 1.0 / root;
+    F[((size_t)pc * rows + k) * w] = root;
+    trace = 0.0; best = 0.0; best_pos = -1; best_key = INT_MAX;
+    for (int p = k + 1; p < n; ++p) {
+      const int col = p == q ? front : perm[p];
+      const double* fc = F + (size_t)col * rows * w; const double* fp = F + (size_t)pc * rows * w;
+      const double* g = G + ((int64_t)col + (int64_t)pc * ldg) * w;          /* row = this column, column = pivot column */
+      for (int t = 0; t < 128; ++t) {
+        double ar = t == 0 ? g[0] : 0.0, ai = (t == 0 && cplx) ? g[1] : 0.0;
+        for (int m = t; m < k; m += 128) {
+          if (cplx) {
+            const double ax = fc[2 * m], ay = fc[2 * m + 1], bx = fp[2 * m], by = fp[2 * m + 1];
+            const double nr = fma(-ax, bx, fma(-ay, by, ar)), ni = fma(-ax, by, fma(ay, bx, ai));
+            ar = nr; ai = ni;
+          } else ar = fma(-fc[m], fp[m], ar);
+        }
+        re[t] = ar; im[t] = ai;
+      }
+      double wr = k > 0 ? tree128(re) : re[0], wi = cplx ? (k > 0 ? tree128(im) : im[0]) : 0.0;
+      double d = D[col];
+      if (cplx) { const double rr = rinv * wr, ri = -rinv * wi; d = fma(-rr, rr, fma(-ri, ri, d)); F[((size_t)col * rows + k) * 2] = rr; F[((size_t)col * rows + k) * 2 + 1] = ri; }
+      else { const double rc = rinv * wr; d = fma(-rc, rc, d); F[(size_t)col * rows + k] = rc; }
+      D[col] = d; trace += d;
+      const int l = p - k;
+      const int key = (j > 0 && l == j) ? chol_key(0, 0) : (j > 0 ? chol_key(l - (l > j ? 1 : 0) - 1, 1) : chol_key(l - 1, 1));
+      if (d > 0.0 && (best_pos < 0 || best < d || (best == d && key < best_key))) { best = d; best_pos = p; best_key = key; }
+    }
+    perm[q] = front; perm[k] = pc;
+  }
+  for (int x = 0; x < n; ++x) {
+    jpiv[x] = perm[x] + 1;
+    for (int kk = 0; kk < rank && kk < rows; ++kk)
+      for (int c = 0; c < w; ++c) R[((int64_t)kk + (int64_t)x * ldr) * w + c] = kk <= x ? F[((size_t)perm[x] * rows + kk) * w + c] : 0.0;
+  }
+  free(F); free(D); free(perm);
+  return rank;
+}

@@ -5,7 +5,12 @@ Run on a machine with a B200 and the reference library built:
 and copy the .npz files it writes next to this script.  Every fixture stores the seeded input matrix and the
 reference's stage outputs for it (column exponents, packed integer Gram, Gram format, raw Gram bytes) plus the
 results of its fits (rank, singular values, one-based pivots).  The CPU tests check the oracle against them.
+
+The cholesky_*.npz fixtures hold the reference's pivoted Cholesky of the Gram matrices of tests/helpers.py
+(CHOLESKY_CASES, rebuilt exactly from the case name): rank, one-based pivots, the diagonal of the factor and the
+SHA-256 of the factor's upper trapezoid (position-major, rows <= position), plus the whole factor for n <= 100.
 """
+
 import os
 import sys
 
@@ -72,6 +77,22 @@ def main(out_dir):
         print(name, "u", u, "lp", lp, "gtype", gtype, "rank", rank, "irank", irank)
     ref.h.GramSegmentK = 8192
     ref.h.GramMatrixAlgorithm = b"A"
+    from tests.helpers import CHOLESKY_CASES, cholesky_case, factor_digest
+    for name in CHOLESKY_CASES:
+        G, cap, eps = cholesky_case(name)
+        n = G.shape[0]
+        cplx = np.iscomplexobj(G)
+        gtype = api.F64_COMPLEX if cplx else api.F64
+        dG = torch.from_numpy(np.ascontiguousarray(G.T)).cuda()             # column-major
+        jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+        X = torch.zeros((cap, n), dtype=dG.dtype, device="cuda")
+        rank = ref.ginterp(eps, n, cap, gtype, X, n, jp, gtype, dG, n)      # overwrites dG: rows < rank of the upper triangle
+        torch.cuda.synchronize()
+        R = dG.cpu().numpy()[:, :rank].T.copy()                              # R[k, x]
+        R[np.arange(rank)[:, None] > np.arange(n)[None, :]] = 0
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), rank=rank, jpiv=jp.cpu().numpy(), diag=np.diagonal(R).real.copy(),
+                            digest=factor_digest(R), R=R if n <= 100 else np.zeros((0, 0)))
+        print(name, "n", n, "cap", cap, "rank", rank)
     ref.destroy()
 
 

@@ -58,3 +58,46 @@ def half_roundtrip(A, atype):
     if atype & 1:
         return (A.real.astype(np.float16).astype(np.float32) + 1j * A.imag.astype(np.float16).astype(np.float32)).astype(np.complex64)
     return A.astype(np.float16).astype(np.float32)
+
+
+# ---- Gram matrices for the pivoted-Cholesky fixtures ----------------------------------------------------------------
+# Every entry is an exact sum of dyadic numbers well inside 53 bits, so the matrix has the same bits whatever BLAS or
+# summation order builds it; the fixtures therefore store only the case name, not the matrix.
+CHOLESKY_CASES = {
+    # name: (kind, complex, n, cap, eps)
+    "chol_f64_toeplitz": ("toeplitz", False, 96, 96, 1e-7),          # constant diagonal: ties at nearly every step
+    "chol_f64c_toeplitz": ("toeplitz", True, 130, 130, 1e-7),
+    "chol_f64_product_420": ("product", False, 420, 420, 1e-5),      # 280 steps: chains of up to three terms
+    "chol_f64_product_cap": ("product", False, 200, 50, 1e-9),       # stopped by the column cap
+    "chol_f64c_product_240": ("product", True, 240, 240, 1e-5),     # 160 steps
+    "chol_f64_last_column": ("product_full", False, 40, 40, 1e-14),  # full rank with K = N: the last column is counted
+}
+
+
+def cholesky_case(name):
+    """(G, cap, eps) of a fixture case; G is n x n, float64 or complex128, Hermitian positive semi-definite."""
+    kind, cplx, n, cap, eps = CHOLESKY_CASES[name]
+    idx = np.arange(n)
+    if kind == "toeplitz":
+        G = 0.5 ** np.abs(idx[:, None] - idx[None, :]).astype(np.float64)
+        if cplx:                                                      # phase i^(row - column): exact, Hermitian
+            G = G * np.array([1, 1j, -1, -1j])[(idx[:, None] - idx[None, :]) % 4]
+        return G, cap, eps
+    rng = np.random.default_rng(sum(map(ord, name)))
+    rows = n if kind == "product_full" else (2 * n) // 3
+    B = rng.integers(-15, 16, size=(rows, n)).astype(np.float64)
+    if cplx:
+        B = B + 1j * rng.integers(-15, 16, size=(rows, n))
+    shift = np.zeros(rows) if kind == "product_full" else np.floor(14.0 * np.arange(rows) / rows)
+    B = B * (2.0 ** -shift)[:, None]                                  # row weights 1 ... 2^-13: G spans 2^-26, exact
+    return B.conj().T @ B, cap, eps
+
+
+def factor_digest(R):
+    """SHA-256 over the bytes of the factor's upper trapezoid, position by position: R[0..min(x, rank - 1), x]."""
+    import hashlib
+    h = hashlib.sha256()
+    rank, n = R.shape
+    for x in range(n):
+        h.update(np.ascontiguousarray(R[:min(x + 1, rank), x]).tobytes())
+    return h.hexdigest()

@@ -345,6 +345,30 @@ def test_pivoted_cholesky_ties_are_broken_like_the_reference(hy, ref, gtype, n, 
     _compare_cholesky(hy, ref, t, gtype, n, cap, 1e-3 if base == api.F32 else 1e-7)
 
 
+@pytest.mark.parametrize("cplx,n,cap,eps", [(False, 700, 700, 1e-9), (False, 513, 300, 1e-12), (True, 400, 400, 1e-9), (False, 1, 1, 1e-9),
+                                            (False, 2, 2, 1e-9), (True, 129, 129, 1e-13)])
+def test_pivoted_cholesky_matches_cpu_oracle(hy, cplx, n, cap, eps):
+    """FP64 and complex FP64 Gram matrices: rank, pivots and every bit of the factor equal the CPU restatement of the
+    reference's kernel (oracle.pivoted_cholesky, itself pinned to factors recorded from the reference library)."""
+    torch = _torch()
+    from oracle import oracle as O
+    rng = np.random.default_rng(4000 + n)
+    gtype = api.F64_COMPLEX if cplx else api.F64
+    dG = _synthetic_gram(rng, n, gtype, 7.0)
+    G = dG.cpu().numpy().T.copy()
+    want_rank, want_jp, want_R = O.pivoted_cholesky(G, cap, eps)
+    jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+    R = torch.zeros((n, cap), dtype=dG.dtype, device="cuda")               # cap x N, column-major
+    rank = hy.pivoted_cholesky(eps, n, cap, gtype, dG, n, jp, R, cap)
+    torch.cuda.synchronize()
+    assert rank == want_rank, (rank, want_rank)
+    np.testing.assert_array_equal(jp.cpu().numpy(), want_jp)
+    rows = min(rank, cap)
+    got = np.ascontiguousarray(R.cpu().numpy().T[:rows])
+    np.testing.assert_array_equal(got.view(np.uint8), np.ascontiguousarray(want_R[:rows]).view(np.uint8))
+    assert hy.status() == 0
+
+
 def test_pivoted_cholesky_counts_a_last_single_column(hy, ref):
     """With K = N the loop stops when one column is left and counts it (src/hyacin_potrfp.cu:264,269 of the
     reference): a full-rank matrix gives rank N and a complete factor."""

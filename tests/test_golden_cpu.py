@@ -8,8 +8,10 @@ import numpy as np
 import pytest
 
 from oracle import oracle as O
+from tests.helpers import CHOLESKY_CASES, cholesky_case, factor_digest
 
-FIXTURES = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "*.npz")))
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FIXTURES = sorted(p for p in glob.glob(os.path.join(GOLDEN, "*.npz")) if not os.path.basename(p).startswith("chol_"))
 
 
 def test_fixtures_are_present():
@@ -51,3 +53,22 @@ def test_recorded_fit_agrees_with_lapack(path):
     assert np.max(np.abs(got - s[:rank])) <= tol * s[0]
     jp = f["jpiv"]
     assert sorted(jp.tolist()) == list(range(1, A.shape[1] + 1))      # a permutation, one-based
+
+
+@pytest.mark.parametrize("name", sorted(CHOLESKY_CASES))
+def test_oracle_cholesky_reproduces_reference_factor(name):
+    """The restated pivoted Cholesky gives the recorded rank, every recorded pivot and every bit of the factor the
+    reference's kernel left in its Gram matrix (src/hyacin_potrfp.cu:214-272), on matrices with ties at nearly every
+    step, with more steps than chains, with a column cap, and with a counted last column."""
+    path = os.path.join(GOLDEN, name + ".npz")
+    assert os.path.exists(path), "fixture missing: run tests/golden/make_golden.py on a B200"
+    f = np.load(path)
+    G, cap, eps = cholesky_case(name)
+    rank, jpiv, R = O.pivoted_cholesky(G, cap, eps)
+    assert rank == int(f["rank"])
+    np.testing.assert_array_equal(jpiv, f["jpiv"])
+    R = np.ascontiguousarray(R[:rank])
+    np.testing.assert_array_equal(np.diagonal(R).real, f["diag"])
+    if f["R"].size:
+        np.testing.assert_array_equal(R.view(np.uint8), np.ascontiguousarray(f["R"]).view(np.uint8))
+    assert factor_digest(R) == str(f["digest"])
