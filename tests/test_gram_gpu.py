@@ -86,6 +86,29 @@ def test_exponents_and_integer_gram_match_oracle(hy, atype, m, n, pad, seg_k, ze
     hy.h.GramSegmentK = 8192
 
 
+def test_row_groups_reconstructed_separately_add_up_exactly(hy, ref):
+    """FP32 input at eps 1e-5 over more than 2^17 rows needs 65 bits in one piece (9 moduli) but 63 bits per 65536-row
+    group (8 moduli): the schedule then reconstructs every group on its own and adds them.  The packed integer Gram
+    equals the CPU oracle and the reference library (which flushes every 65536 rows here) bit for bit."""
+    torch = _torch()
+    rng = np.random.default_rng(99)
+    m, n, atype, eps = (1 << 17) + 300, 24, api.F32, 1e-5
+    A = random_matrix(rng, m, n, atype)
+    dA = to_device_colmajor(A, None, atype)
+    u, cp, lp, tri = hy.herk_batch_init(eps, m, n, atype)
+    plan = hy.crt_plan(u, 0, m)
+    assert plan["group_rows"] == 65536 and plan["moduli"] == 8, plan
+    segs, vexp = _run_exponents(hy, dA, m, n, m, atype, u)
+    C = _run_herk(hy, dA, m, n, m, atype, u, lp, cp, segs, vexp)
+    want_vexp = O.column_exponents(A, atype, u, *segs)
+    np.testing.assert_array_equal(vexp.cpu().numpy(), want_vexp)
+    np.testing.assert_array_equal(C.cpu().numpy().view(np.uint64), O.gram_exact(A, atype, want_vexp[0], lp))
+    C_ref = torch.zeros_like(C)
+    ref.herk_batch(segs[0], segs[1], segs[2], n, atype, dA, m, u, vexp, 0, lp, C_ref)
+    torch.cuda.synchronize()
+    assert torch.equal(C, C_ref)
+
+
 def test_beta_accumulates_and_row_blocks_add_up(hy):
     """C(beta=1) over two row blocks equals C over the stacked matrix (the hook used to stream a tall matrix)."""
     torch = _torch()
