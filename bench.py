@@ -45,8 +45,8 @@ PEAKS = os.path.join(ROOT, "MEASURED_PEAKS.json")
 # DRAM traffic of the Gram kernel from an ncu capture of a smaller launch (16384 rows, 13 moduli, N = 4096):
 # 1.92 GB read and 116 MB written.  Reads grow in proportion to rows x moduli (9016 bytes per row and modulus),
 # the residue bytes written (and re-read when accumulating) depend on N and the moduli only.
-GRAM_DRAM_READ_BYTES_PER_ROW_MODULUS = 9016.0
-GRAM_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 16384-row launch (profiles/gram_pair_kernel_n4096_rows16384.txt), reads scaled by rows"
+GRAM_DRAM_READ_BYTES_PER_ROW_MODULUS = 8945.0
+GRAM_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 16384-row launch (profiles/gram_wide_kernel_n4096_rows16384.txt), reads scaled by rows"
 
 
 def parse():
@@ -508,7 +508,7 @@ def main():
             peak, src = 2.0 * 1400.0, "2 x fallback sustained dense bf16 (1.4 PFLOP/s)"
         q_ms = prof["quantize_ms"] / max(prof["quantize_launches"], 1)
         out["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                           "traffic": None, "kernel": "gram_pair_kernel: residue Gram (tcgen05.mma.cta_group::2 kind::i8)", "avg_launch_ms": avg_ms,
+                           "traffic": None, "kernel": "gram_wide_kernel: residue Gram (tcgen05.mma.cta_group::2 kind::i8, two 256 x 256 tiles per CTA pair)", "avg_launch_ms": avg_ms,
                            "launches_timed": prof["gram_launches"], "ops_per_launch": alg_ops, "moduli_required": need_moduli, "moduli_issued": plan["moduli"],
                            "issued_tops": issued_ops / (avg_ms * 1e-3) / 1e12, "frac_issued": issued_ops / (avg_ms * 1e-3) / 1e12 / peak,
                            "peak_source": src, "int8_peak": int8_peak,

@@ -32,6 +32,7 @@ B200_SYMBOLS = [
     "hyacinB200GramResidues", "hyacinB200Reconstruct", "hyacinB200LaunchCount", "hyacinB200ProfileEnable",
     "hyacinB200ProfileRead", "hyacinB200SlicePlan", "hyacinB200HerkBatchStatic", "hyacinB200QuantizeLimbs", "hyacinB200GramLimbs",
     "hyacinB200DequantizeViaSlices", "hyacinB200ProfileReadTail", "hyacinB200PivotedCholesky", "hyacinB200SelfTestWait", "hyacinB200VectorRange",
+    "hyacinB200GramItem",
 ]
 
 
@@ -92,6 +93,7 @@ def load(path: str | None = None) -> ctypes.CDLL:
         "hyacinB200VectorRange": (None, [H, i32, i32, i32, vp, vp]),
         "hyacinB200SelfTestWait": (i32, [H, c_uint32, c_uint32]),
         "hyacinB200PivotedCholesky": (i32, [H, f64, i32, i32, i32, vp, i32, vp, vp, i32]),
+        "hyacinB200GramItem": (i32, [i32, i32, i32, i32, i32, i32, i32, POINTER(i32), POINTER(i32), POINTER(i32), POINTER(i32)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name, None)
@@ -101,6 +103,17 @@ def load(path: str | None = None) -> ctypes.CDLL:
             continue
         fn.restype, fn.argtypes = res, args
     return lib
+
+
+def gram_items(tiles_x: int, pair_rows: int, full: bool, moduli: int, pairs: int, pair: int, lib=None):
+    """Work items (modulus, tile_row, tile_col, width) of one CTA pair of the residue Gram kernel, in order."""
+    lib = lib or load()
+    m, ty, tx, w = c_int32(), c_int32(), c_int32(), c_int32()
+    out, k = [], 0
+    while lib.hyacinB200GramItem(tiles_x, pair_rows, 1 if full else 0, moduli, pairs, pair, k, byref(m), byref(ty), byref(tx), byref(w)):
+        out.append((m.value, ty.value, tx.value, w.value))
+        k += 1
+    return out
 
 
 def _dp(t) -> c_void_p:

@@ -5,10 +5,11 @@
 // reduction is the epilogue of the GEMM tile, so the only thing that leaves the SM is one byte per
 // (entry, modulus).
 //
-// Two kernels.  gram_pair_kernel (further down) is the one the CRT route runs: clusters of two CTAs on 256 x 256
-// tiles with tcgen05.mma.cta_group::2.  gram_kernel<LIMBS> is the single-CTA form (128 x 256 tiles); it carries
-// the limb route and is the fallback of the CRT route.  Structure of the single-CTA form (one CTA per SM,
-// persistent over (modulus, tile) work items):
+// Three kernels.  gram_wide_kernel (last in the file) is the one the CRT route runs: clusters of two CTAs with
+// tcgen05.mma.cta_group::2 on items of two neighbouring 256 x 256 tiles that share their A rows.  gram_pair_kernel is
+// its predecessor on single 256 x 256 tiles (kept for A/B runs and as the fallback).  gram_kernel<LIMBS> is the
+// single-CTA form (128 x 256 tiles); it carries the limb route and is the last fallback of the CRT route.  Structure
+// of the single-CTA form (one CTA per SM, persistent over (modulus, tile) work items):
 //   warp 0     TMA producer: 128-byte-swizzled K-major boxes of the A operand (128 Gram rows) and the B
 //              operand (256 Gram columns) into a 4-stage shared-memory ring, completion on mbarriers;
 //   warp 1     MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::i8 (M128 N256 K32) on shared-memory
@@ -17,7 +18,7 @@
 //   warps 2-5  epilogue: tcgen05.ld of the int32 accumulator (32 lanes x 32 columns per load), reduction
 //              modulo m, optional accumulation onto the residues of earlier row chunks, 32-byte stores.
 // The two TMEM buffers let the epilogue of one tile overlap the main loop of the next.
-// No TMA load in this file uses cluster multicast (tcgen05.commit of the pair kernel does address both CTAs of
+// No TMA load in this file uses cluster multicast (tcgen05.commit of the two-CTA kernels does address both CTAs of
 // its pair).  Every wait is bounded: a wait that expires raises a status word for the host and makes all roles
 // leave their loops so that TMEM is still released.
 #include "hyb_internal.h"
@@ -468,6 +469,197 @@ gram_pair_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
+// ---- two-CTA variant on items of two neighbouring tiles (the default of the CRT route) ----------------------------
+// A CTA pair works on the pair tiles (TY, TX) and (TY, TX + 1) at once: the 128 A rows a CTA stages are multiplied with
+// both column blocks (two MMAs per K step, one accumulator each), so a CTA stages 48 KiB per 128-byte K block for two
+// accumulators instead of 64 KiB.  The step runs against the power cap, so fewer bytes moved per MAC means a higher
+// clock: 5 % on the step against gram_pair_kernel.  All 512 columns of tensor memory hold one item, so the accumulators
+// are not double buffered: the epilogue (eight warps, both accumulators in parallel, the old residue bytes of the next
+// 32 columns prefetched) runs between items, about 1 % of a 65536-row item.  A tile row with an odd number of tiles ends
+// in an ordinary single-tile item.  Items of two sizes are dealt so that all pairs finish together: the double items
+// round-robin, then the single ones first to the pairs that got one double item less (WideSchedule; the host mirror
+// hyacinB200GramItem lets a CPU test check that every tile is covered once).  HYACIN_B200_GRAM_WIDE=0 selects
+// gram_pair_kernel instead.
+constexpr int kStagesW = 4;
+constexpr uint32_t kStageBytesW = 3 * kABytes;               // A rows + two blocks of B columns per CTA
+constexpr size_t kSmemBytesW = 1024 + size_t(kStagesW) * kStageBytesW + 256;
+constexpr int kEpilogueWarpsW = 8;
+constexpr int kThreadsW = 64 + 32 * kEpilogueWarpsW;
+struct BarriersW {
+  uint64_t full[kStagesW], empty[kStagesW], acc_full, acc_empty;
+  uint32_t tmem_base; uint32_t abort_flag;
+};
+
+struct WideSchedule {
+  int tiles_x, pair_rows, full, clusters, cluster;
+  int doubles_per_plane, singles_per_plane, doubles, singles;
+  int my_doubles, low_first, low_count, filled, my_filled;
+  // full = 0: pair tiles TY <= TX of the upper triangle; full = 1: all pair_rows x tiles_x pair tiles
+  __host__ __device__ void init(int tiles_x_, int pair_rows_, int full_, int moduli, int clusters_, int cluster_) {
+    tiles_x = tiles_x_; pair_rows = pair_rows_; full = full_; clusters = clusters_; cluster = cluster_;
+    doubles_per_plane = full ? pair_rows * (tiles_x / 2) : (tiles_x * tiles_x) / 4;
+    singles_per_plane = full ? (tiles_x & 1) * pair_rows : (tiles_x + 1) / 2;
+    doubles = moduli * doubles_per_plane; singles = moduli * singles_per_plane;
+    const int r = doubles % clusters;
+    my_doubles = doubles / clusters + (cluster < r ? 1 : 0);
+    // pairs r .. clusters - 1 have one double item less: they take up to two single items each before the rest is dealt to all
+    low_first = r; low_count = clusters - r;
+    filled = r > 0 ? (singles < 2 * low_count ? singles : 2 * low_count) : 0;
+    my_filled = 0;
+    if (r > 0 && cluster >= r) my_filled = (cluster - r < filled ? 1 : 0) + (cluster - r + low_count < filled ? 1 : 0);
+  }
+  // k-th item of this pair: modulus, tile row, first tile column, number of tiles (1 or 2); false when there is none
+  __host__ __device__ bool item(int k, int* m, int* TY, int* TX, int* width) const {
+    if (k < my_doubles) {
+      const int g = cluster + k * clusters;
+      *m = g / doubles_per_plane; int w = g - *m * doubles_per_plane;
+      if (full) { const int per_row = tiles_x / 2; *TY = w / per_row; *TX = 2 * (w - *TY * per_row); }
+      else for (int ty = 0;; ++ty) { const int c = (tiles_x - ty) / 2; if (w < c) { *TY = ty; *TX = ty + 2 * w; break; } w -= c; }
+      *width = 2; return true;
+    }
+    const int j = k - my_doubles;
+    const int sidx = j < my_filled ? cluster - low_first + j * low_count : filled + cluster + (j - my_filled) * clusters;
+    if (sidx >= singles) return false;
+    *m = sidx / singles_per_plane; const int w = sidx - *m * singles_per_plane;
+    *TY = full ? w : ((tiles_x - 1) & 1) + 2 * w; *TX = tiles_x - 1; *width = 1;
+    return true;
+  }
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsW, 1)
+gram_wide_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ GramParams p, int tiles_x) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  BarriersW* bars = reinterpret_cast<BarriersW*>(aligned + size_t(kStagesW) * kStageBytesW);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  WideSchedule sched; sched.init(tiles_x, (p.tiles_y + 1) / 2, p.full, p.moduli, gridDim.x >> 1, blockIdx.x >> 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesW; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    mbar_init(&bars->acc_full, 1); mbar_init(&bars->acc_empty, 2 * kEpilogueWarpsW);
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs: own rows and own halves of the column blocks) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0; bool ok = true;
+      int m, TY, TX, width;
+      for (int k = 0; ok && sched.item(k, &m, &TY, &TX, &width); ++k) {
+        const int y0 = (2 * TY + int(rank)) * kTileY, x0 = TX * kTileX + int(rank) * kTileY;
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag, p.status, 21u))) break;
+          if (rank == 0) mbar_expect_tx(&bars->full[stage], 2u * uint32_t(1 + width) * kABytes);
+          const uint32_t sa = base + stage * kStageBytesW;
+          const uint32_t full0 = map_to_cta(smem_u32(&bars->full[stage]), 0);
+          tma_load_3d_pair(sa, &tmap, full0, p.ka0 + kb * kStageK, y0, m);
+          tma_load_3d_pair(sa + kABytes, &tmap, full0, p.kb0 + kb * kStageK, x0, m);
+          if (width == 2) tma_load_3d_pair(sa + 2 * kABytes, &tmap, full0, p.kb0 + kb * kStageK, x0 + kTileX, m);
+          if (++stage == kStagesW) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t stage = 0, phase = 0, acc_phase = 0; bool ok = true;
+      int m, TY, TX, width;
+      for (int k = 0; ok && sched.item(k, &m, &TY, &TX, &width); ++k) {
+        if (!(ok = mbar_wait(&bars->acc_empty, acc_phase ^ 1u, abort_flag, p.status, 22u))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          if (!(ok = mbar_wait(&bars->full[stage], phase, abort_flag, p.status, 23u))) break;
+          tc_fence_after();
+          const uint32_t sa = base + stage * kStageBytesW;
+          const uint64_t adesc = smem_desc_k128(sa), b0desc = smem_desc_k128(sa + kABytes), b1desc = smem_desc_k128(sa + 2 * kABytes);
+#pragma unroll
+          for (int q = 0; q < kStageK / kUmmaK; ++q) {
+            umma_i8_pair(tmem_base, adesc + uint64_t(2 * q), b0desc + uint64_t(2 * q), kInstrDesc2, (kb | q) != 0 ? 1u : 0u);
+            if (width == 2) umma_i8_pair(tmem_base + kTileX, adesc + uint64_t(2 * q), b1desc + uint64_t(2 * q), kInstrDesc2, (kb | q) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&bars->empty[stage]);
+          if (++stage == kStagesW) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&bars->acc_full);
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps (both CTAs: own 128 rows; warps 2-5 and 6-9 split the columns) ----------------
+    const int lane_group = warp & 3, half = (warp - 2) >> 2;
+    const int row = lane_group * 32 + lane;
+    uint32_t acc_phase = 0; bool ok = true;
+    int m, TY, TX, width;
+    for (int k = 0; ok && sched.item(k, &m, &TY, &TX, &width); ++k) {
+      const int ty = 2 * TY + int(rank);
+      ok = mbar_wait(&bars->acc_full, acc_phase, abort_flag, p.status, 24u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (ty < p.tiles_y) {
+        // double item: this warp drains one accumulator (one tile); single item: half of the only accumulator
+        const int col0 = width == 2 ? half * kTileX : half * (kTileX / 2), chunks = width == 2 ? kTileX / 32 : kTileX / 64;
+        const int tx = width == 2 ? TX + half : TX, out_col0 = width == 2 ? 0 : col0;
+        const uint32_t taddr = tmem_base + (uint32_t(lane_group * 32) << 16) + uint32_t(col0);
+        const int tile = p.full ? ty + tx * p.tiles_y : tile_index(p.tiles_y, ty, tx);
+        const uint32_t modulus = p.k.modulus[m], magic = p.k.magic[m], bias = p.k.bias[m];
+        uint8_t* out = p.residues + (size_t(m) * p.num_tiles + tile) * size_t(kTileY * kTileX) + size_t(row) * kTileX + out_col0;
+        uint4 old0 = make_uint4(0, 0, 0, 0), old1 = old0;
+        if (p.accumulate) { old0 = *reinterpret_cast<const uint4*>(out); old1 = *reinterpret_cast<const uint4*>(out + 16); }
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          const uint32_t oldw[8] = {old0.x, old0.y, old0.z, old0.w, old1.x, old1.y, old1.z, old1.w};
+          if (p.accumulate && c + 1 < chunks) {          // the bytes of the next chunk arrive while this one is reduced
+            old0 = *reinterpret_cast<const uint4*>(out + (c + 1) * 32); old1 = *reinterpret_cast<const uint4*>(out + (c + 1) * 32 + 16);
+          }
+          tmem_ld_wait();
+          uint32_t packed[8];
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              uint32_t t = v[w * 4 + b] + bias + ((oldw[w] >> (8 * b)) & 0xFFu);
+              uint32_t r = t - __umulhi(t, magic) * modulus;
+              r = r >= modulus ? r - modulus : r;
+              word |= r << (8 * b);
+            }
+            packed[w] = word;
+          }
+          *reinterpret_cast<uint4*>(out + c * 32) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(out + c * 32 + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&bars->acc_empty), 0));
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
 // ---- host side ------------------------------------------------------------------------------------
 }  // namespace
 
@@ -524,6 +716,19 @@ void launch_gram_residues(cudaStream_t stream, const GramLaunch& g) {
     p.k.bias[i] = (0x80000000u / m) * m;
   }
   static const bool single_cta = [] { const char* e = std::getenv("HYACIN_B200_GRAM_SINGLE_CTA"); return e && e[0] == '1'; }();   // diagnosis: A/B the two kernels
+  static const bool narrow = [] { const char* e = std::getenv("HYACIN_B200_GRAM_WIDE"); return e && e[0] == '0'; }();        // diagnosis: items of one tile
+  if (!narrow && !single_cta && p.num_kblocks > 0 && g.sm_count >= 2) {
+    // CTA pairs on items of two neighbouring 256 x 256 tiles
+    HYB_CUDA(cudaFuncSetAttribute(gram_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytesW)));
+    const int units = g.moduli * (p.full ? ((tp.tiles_y + 1) / 2) * tp.tiles_x : tp.tiles_x * (tp.tiles_x + 1) / 2);
+    int clusters = g.sm_count / 2; if (clusters > units) clusters = units;
+    ProfileScope prof(stream, KernelKind::Gram);
+    count_launch();
+    gram_wide_kernel<<<2 * clusters, kThreadsW, kSmemBytesW, stream>>>(tmap, p, tp.tiles_x);
+    const cudaError_t launched = cudaGetLastError();
+    if (launched == cudaSuccess) return;
+    std::fprintf(stderr, "hyacin-b200: cluster launch of the wide Gram kernel refused (%s); trying the pair kernel\n", cudaGetErrorString(launched));
+  }
   if (!single_cta && p.num_kblocks > 0 && g.sm_count >= 2) {
     // CTA pairs on 256 x 256 tiles; the single-CTA kernel below remains for devices that report one SM
     HYB_CUDA(cudaFuncSetAttribute(gram_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes2)));
@@ -568,6 +773,12 @@ void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g) {
   gram_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
   if (p.split) limb_combine_kernel<<<dim3(tp.num_tiles, kTileX / 32), kTileY, 0, stream>>>(p);
   HYB_CUDA(cudaGetLastError());
+}
+
+bool gram_schedule_item(int tiles_x, int pair_rows, int full, int moduli, int clusters, int cluster, int k, int* m, int* TY, int* TX, int* width) {
+  if (tiles_x <= 0 || pair_rows <= 0 || moduli <= 0 || clusters <= 0 || cluster < 0 || cluster >= clusters || k < 0) return false;
+  WideSchedule sched; sched.init(tiles_x, pair_rows, full ? 1 : 0, moduli, clusters, cluster);
+  return sched.item(k, m, TY, TX, width);
 }
 
 size_t gram_limbs_scratch_bytes(int n, int order, int sm_count) {

@@ -401,6 +401,14 @@ extern "C" void hyacinB200VectorRange(const hyacinHandle_t* handle, int32_t batc
   hyb::launch_vector_range(handle->cudaStream, batches, N, u, vexp, segU);
 }
 
+extern "C" int32_t hyacinB200GramItem(int32_t tilesX, int32_t pairRows, int32_t full, int32_t moduli, int32_t pairs, int32_t pair, int32_t k,
+                                      int32_t* modulus, int32_t* tileRow, int32_t* tileCol, int32_t* width) {
+  int m = 0, ty = 0, tx = 0, w = 0;
+  if (!hyb::gram_schedule_item(tilesX, pairRows, full, moduli, pairs, pair, k, &m, &ty, &tx, &w)) return 0;
+  if (modulus) *modulus = m; if (tileRow) *tileRow = ty; if (tileCol) *tileCol = tx; if (width) *width = w;
+  return 1;
+}
+
 extern "C" void hyacinB200TileInfo(int32_t N, int32_t* tileY, int32_t* tileX, int32_t* tilesY, int32_t* numTiles) {
   const hyb::TilePlan tp = hyb::make_tile_plan(N);
   if (tileY) *tileY = hyb::kTileY; if (tileX) *tileX = hyb::kTileX;

@@ -140,6 +140,8 @@ struct GramLimbLaunch {
 void launch_gram_limbs(cudaStream_t stream, const GramLimbLaunch& g);
 // Scratch that lets launch_gram_limbs fill the GPU when the Gram has fewer tiles than the device has SMs (0 otherwise).
 size_t gram_limbs_scratch_bytes(int n, int order, int sm_count);
+// k-th work item of CTA pair `cluster` in the residue Gram kernel (host mirror of the device schedule, for tests)
+bool gram_schedule_item(int tiles_x, int pair_rows, int full, int moduli, int clusters, int cluster, int k, int* m, int* TY, int* TX, int* width);
 // Quantise rows of A into `order` planes of balanced base-256 digits (same plane layout as launch_quantize_crt).
 // Reference counterpart: src/quantize_limbs.cu:29-79.
 void launch_quantize_limbs(cudaStream_t stream, hyacinPrecision_t atype, int rows, int n, const void* A, int64_t lda,

@@ -46,6 +46,14 @@ void hyacinB200VectorRange(const hyacinHandle_t* handle, int32_t batches, int32_
  * tiles that touch the upper triangle.  A residue buffer holds moduli * numTiles * tileY * tileX bytes. */
 void hyacinB200TileInfo(int32_t N, int32_t* tileY, int32_t* tileX, int32_t* tilesY, int32_t* numTiles);
 
+/* Work schedule of the residue Gram kernel (host mirror, no GPU needed): the k-th item of CTA pair `pair` out of `pairs`
+ * when `moduli` planes of tilesX column blocks of 256 are multiplied.  An item is `width` (1 or 2) neighbouring 256 x 256
+ * tiles of one tile row: (tileRow, tileCol) and, for width 2, (tileRow, tileCol + 1).  full = 0: tiles tileRow <= tileCol of
+ * the upper triangle (pairRows is ignored); full = 1: all pairRows x tilesX tiles.  Returns 0 when the pair has fewer than
+ * k + 1 items.  Over all pairs every tile of every plane appears exactly once. */
+int32_t hyacinB200GramItem(int32_t tilesX, int32_t pairRows, int32_t full, int32_t moduli, int32_t pairs, int32_t pair, int32_t k,
+                           int32_t* modulus, int32_t* tileRow, int32_t* tileCol, int32_t* width);
+
 /* Quantise `rows` rows of A (column-major, lda in elements) into int8 residue planes
  * W[modulus][column][part * ldk + row]; ldk is a multiple of 128 and rows [rows, ldk) are zero-filled.
  * Real input: one part.  Complex input: three parts (re, im, -re).

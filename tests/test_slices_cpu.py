@@ -91,3 +91,31 @@ def test_two_rank_sum_of_slices_equals_exact_limb_sum(order):
     for r in res:
         want = [O.limbs_to_int([exact[l, i] for l in range(order)], order) for i in range(exact.shape[1])]
         assert r[1] == want
+
+
+@pytest.mark.parametrize("full", [False, True])
+def test_gram_schedule_covers_every_tile_once_and_is_balanced(full):
+    """The residue Gram kernel deals items of one or two 256 x 256 tiles to its CTA pairs: over all pairs every tile
+    of every modulus plane appears exactly once, items stay inside the tile grid, and no pair gets more than one tile
+    above the even share (host mirror of the device schedule; 74 pairs = one B200)."""
+    from hyacinth_b200 import api
+    lib = api.load()
+    for tiles_x in (1, 2, 3, 4, 7, 8, 16, 17, 32):
+        pair_rows = tiles_x if not full else max(1, tiles_x - 1)        # a full product may have fewer tile rows
+        for moduli in (1, 8, 13, 15):
+            for pairs in (1, 2, 5, 74):
+                seen, loads = set(), []
+                for pair in range(pairs):
+                    items = api.gram_items(tiles_x, pair_rows, full, moduli, pairs, pair, lib)
+                    loads.append(sum(w for *_, w in items))
+                    for m, ty, tx, w in items:
+                        assert w in (1, 2) and 0 <= m < moduli
+                        for d in range(w):
+                            assert (0 <= ty < pair_rows and 0 <= tx + d < tiles_x) if full else (0 <= ty <= tx + d < tiles_x)
+                            assert (m, ty, tx + d) not in seen
+                            seen.add((m, ty, tx + d))
+                total = moduli * (pair_rows * tiles_x if full else tiles_x * (tiles_x + 1) // 2)
+                assert len(seen) == total
+                assert max(loads) <= -(-total // pairs) + 1, (tiles_x, moduli, pairs, max(loads), total / pairs)
+    # the headline case: 13 planes of 136 pair tiles over 74 pairs -> 24 tile-units at most (ideal 23.9)
+    assert max(sum(w for *_, w in api.gram_items(16, 16, False, 13, 74, c, lib)) for c in range(74)) == 24
