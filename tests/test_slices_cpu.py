@@ -119,3 +119,28 @@ def test_gram_schedule_covers_every_tile_once_and_is_balanced(full):
                 assert max(loads) <= -(-total // pairs) + 1, (tiles_x, moduli, pairs, max(loads), total / pairs)
     # the headline case: 13 planes of 136 pair tiles over 74 pairs -> 24 tile-units at most (ideal 23.9)
     assert max(sum(w for *_, w in api.gram_items(16, 16, False, 13, 74, c, lib)) for c in range(74)) == 24
+
+
+def test_crt_plan_groups_rows_when_that_saves_a_modulus():
+    """hyacinB200CrtPlan (host logic): the moduli always cover the bits of one row group, 2 u + 1 + ceil(log2 group), and
+    the group size is the cheaper of 'one more modulus for every row' and 'one more reconstruction per group'."""
+    import math
+    import re
+    lib = api.load()
+    header = open(os.path.join(os.path.dirname(os.path.abspath(api.__file__)), "csrc", "crt_tables.h")).read()
+    bits = [int(v) for v in re.search(r"kRangeBits\[kMaxModuli\] = \{([^}]*)\}", header).group(1).split(",")]
+
+    def plan(u, rows):
+        m, vb, g, c = (ctypes.c_int32() for _ in range(4))
+        lib.hyacinB200CrtPlan(u, 0, ctypes.c_int64(rows), ctypes.byref(m), ctypes.byref(vb), ctypes.byref(g), ctypes.byref(c))
+        return m.value, g.value, c.value
+
+    for u, rows in [(40, 1 << 20), (40, 1 << 22), (40, 1 << 23), (23, 1 << 17), (23, (1 << 17) + 300), (23, 1 << 20), (13, 1 << 20), (40, 512),
+                    (30, 1 << 22), (70, 1 << 20)]:
+        moduli, group, chunk = plan(u, rows)
+        need = 2 * u + 1 + (math.ceil(math.log2(group)) if group > 1 else 0)
+        assert bits[moduli - 1] >= need and (moduli == 1 or bits[moduli - 2] < need), (u, rows, moduli, group)
+        assert group <= rows and chunk <= max(group, 128) and (group == rows or group % chunk == 0)
+    assert plan(40, 1 << 20)[:2] == (13, 1 << 20)            # benchmark configuration 2: one group
+    assert plan(23, 1 << 17)[:2] == (8, 1 << 16)             # configuration 5: two groups of 65536 rows instead of 9 moduli
+    assert plan(40, 1 << 22)[:2] == (13, 1 << 21)            # two groups instead of 14 moduli
