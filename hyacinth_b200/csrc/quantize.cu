@@ -189,20 +189,23 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
       if (i >= p.moduli) break;
       const uint32_t bias = p.k.bias[i], w0 = p.k.weight[i][0], w1 = p.k.weight[i][1], w2 = p.k.weight[i][2];
       const uint32_t magic = p.k.magic[i], modulus = p.k.modulus[i];
+      const uint32_t neg_modulus = 0u - modulus;      // t - q m as one multiply-add
       uint32_t r8[kRows];
 #pragma unroll
       for (int r = 0; r < kRows; ++r) {
+        // modulus 256 (first in the table): the bias 2^(8 nb - 1) is a multiple of 256 for nb > 1, so the low byte of the
+        // biased value is the low byte of q itself, i.e. its centred residue (for nb = 1 the bias is 128 and is flipped
+        // away below); the packing takes only that byte
+        if (i == 0) { r8[r] = w[r][0]; continue; }
         uint32_t t = __dp4a(w[r][0], w0, bias);
         if (NW > 1) t = __dp4a(w[r][1], w1, t);
         if (NW > 2) t = __dp4a(w[r][2], w2, t);
-        // modulus 256 (first in the table): the low byte is the residue and the packing below takes only that byte
-        if (i == 0) r8[r] = t;
-        else if constexpr (!FR) r8[r] = t - __umulhi(t, magic) * modulus;          // exact: t * modulus < 2^32
-        else r8[r] = t - __float_as_uint(fmaf(__uint_as_float(t), __uint_as_float(p.k.fr_inv[i]), __uint_as_float(p.k.fr_add[i]))) * modulus;
+        if constexpr (!FR) r8[r] = __umulhi(t, magic) * neg_modulus + t;           // exact: t * modulus < 2^32
+        else r8[r] = __float_as_uint(fmaf(__uint_as_float(t), __uint_as_float(p.k.fr_inv[i]), __uint_as_float(p.k.fr_add[i]))) * neg_modulus + t;
       }
       // four residues per word by byte permutes (ALU pipe); the integer reduction leaves (q + 128) mod m and needs
-      // -128 per byte, the float reduction leaves the centred residue itself
-      const uint32_t flip = (!FR || i == 0) ? 0x80808080u : 0u;
+      // -128 per byte, the float reduction and modulus 256 leave the centred residue itself
+      const uint32_t flip = (i == 0 ? p.value_bytes == 1 : !FR) ? 0x80808080u : 0u;
       uint2 packed;
       packed.x = __byte_perm(__byte_perm(r8[0], r8[1], 0x0040), __byte_perm(r8[2], r8[3], 0x0040), 0x5410) ^ flip;
       packed.y = __byte_perm(__byte_perm(r8[4], r8[5], 0x0040), __byte_perm(r8[6], r8[7], 0x0040), 0x5410) ^ flip;
