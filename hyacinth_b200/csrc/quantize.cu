@@ -214,6 +214,54 @@ __global__ void __launch_bounds__(256) quantize_crt_kernel(const __grid_constant
   }
 }
 
+// Real input in 'N' orientation, sixteen rows per thread: the per-modulus work of a thread that does not depend on the
+// row (guard, plane address, constants moved to registers) is spread over twice as many values, and every plane receives
+// one 16-byte store per thread (512 contiguous bytes per warp).  The kernel is bound by instruction issue inside the
+// power-capped step, so instructions saved are time saved.
+template <typename T, int NW, bool FR>
+__global__ void __launch_bounds__(256) quantize_crt_rows16_kernel(const __grid_constant__ QuantParams p) {
+  constexpr int kWide = 2 * kRows;
+  const int col = blockIdx.y, row0 = (blockIdx.x * blockDim.x + threadIdx.x) * kWide;
+  if (row0 >= p.ldk) return;
+  const int expon = p.vexp[col];
+  double s1 = 0.0, s2 = 0.0;
+  if (expon != INT_MAX) { int h = expon / 2; s1 = pow2(h); s2 = pow2(expon - h); }
+  const T* src = static_cast<const T*>(p.A) + (int64_t(col) * p.lda + row0);
+  uint32_t w[kWide][3];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    double v[kRows][1];
+    int valid = p.rows - row0 - half * kRows; valid = valid < 0 ? 0 : (valid > kRows ? kRows : valid);
+    load_rows<T, 1>(src + half * kRows, valid, s1, s2, v);
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) biased_words<NW>(v[r][0], p.value_bytes, false, w[half * kRows + r]);
+  }
+  int8_t* out = p.W + int64_t(col) * p.col_pitch + row0;
+#pragma unroll
+  for (int i = 0; i < crt::kMaxModuli; ++i) {
+    if (i >= p.moduli) break;
+    const uint32_t bias = p.k.bias[i], w0 = p.k.weight[i][0], w1 = p.k.weight[i][1], w2 = p.k.weight[i][2];
+    const uint32_t magic = p.k.magic[i], neg_modulus = 0u - p.k.modulus[i];
+    uint32_t r8[kWide];
+#pragma unroll
+    for (int r = 0; r < kWide; ++r) {
+      if (i == 0) { r8[r] = w[r][0]; continue; }              // modulus 256: see quantize_crt_kernel
+      uint32_t t = __dp4a(w[r][0], w0, bias);
+      if (NW > 1) t = __dp4a(w[r][1], w1, t);
+      if (NW > 2) t = __dp4a(w[r][2], w2, t);
+      if constexpr (!FR) r8[r] = __umulhi(t, magic) * neg_modulus + t;
+      else r8[r] = __float_as_uint(fmaf(__uint_as_float(t), __uint_as_float(p.k.fr_inv[i]), __uint_as_float(p.k.fr_add[i]))) * neg_modulus + t;
+    }
+    const uint32_t flip = (i == 0 ? p.value_bytes == 1 : !FR) ? 0x80808080u : 0u;
+    uint4 packed;
+    packed.x = __byte_perm(__byte_perm(r8[0], r8[1], 0x0040), __byte_perm(r8[2], r8[3], 0x0040), 0x5410) ^ flip;
+    packed.y = __byte_perm(__byte_perm(r8[4], r8[5], 0x0040), __byte_perm(r8[6], r8[7], 0x0040), 0x5410) ^ flip;
+    packed.z = __byte_perm(__byte_perm(r8[8], r8[9], 0x0040), __byte_perm(r8[10], r8[11], 0x0040), 0x5410) ^ flip;
+    packed.w = __byte_perm(__byte_perm(r8[12], r8[13], 0x0040), __byte_perm(r8[14], r8[15], 0x0040), 0x5410) ^ flip;
+    *reinterpret_cast<uint4*>(out + int64_t(i) * p.plane_pitch) = packed;
+  }
+}
+
 // ---- complex input, moduli with a square root of -1 -------------------------------------------------------------
 // Every modulus m of the crt2m set has an iota with iota^2 = -1 (mod m), so the complex value re + i im is carried by
 // the two residues p = re - iota im and q = re + iota im, and P^T Q = Re(A^H A) + iota Im(A^H A) (mod m) entry by entry:
@@ -364,6 +412,14 @@ void launch_limbs_typed(cudaStream_t stream, const LimbParams& p) {
 template <typename T, int PARTS, bool FR>
 void launch_typed_fr(cudaStream_t stream, const QuantParams& p) {
   const int nw = (p.value_bytes + 3) / 4;
+  static const bool rows8 = [] { const char* e = std::getenv("HYACIN_B200_QUANT_ROWS"); return e && e[0] == '8'; }();      // diagnosis: A/B the two kernels
+  if (PARTS == 1 && p.op == 0 && !rows8 && p.ldk % (2 * kRows) == 0 && (reinterpret_cast<uintptr_t>(p.W) & 15) == 0 && p.col_pitch % 16 == 0) {
+    dim3 grid(unsigned((p.ldk / (2 * kRows) + 255) / 256), unsigned(p.n));
+    if (nw <= 1) quantize_crt_rows16_kernel<T, 1, FR><<<grid, 256, 0, stream>>>(p);
+    else if (nw == 2) quantize_crt_rows16_kernel<T, 2, FR><<<grid, 256, 0, stream>>>(p);
+    else quantize_crt_rows16_kernel<T, 3, FR><<<grid, 256, 0, stream>>>(p);
+    return;
+  }
   if (p.op == 0) {
     dim3 grid(unsigned((p.ldk / kRows + 255) / 256), unsigned(p.n));
     if (nw <= 1) quantize_crt_kernel<T, 1, PARTS, false, FR><<<grid, 256, 0, stream>>>(p);
