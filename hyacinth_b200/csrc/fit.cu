@@ -99,10 +99,22 @@ bool stage_gemm(const hyacinHandle_t* h, hyacinPrecision_t t, char op, int m, in
   const cublasOperation_t opa = op == 'C' ? (is_complex(t) ? CUBLAS_OP_C : CUBLAS_OP_T) : op == 'T' ? CUBLAS_OP_T : CUBLAS_OP_N;
   switch (int(t)) {
     case HYACIN_F64: { double one = 1., zero = 0.; HYB_LIB(cublasDgemm(b, opa, CUBLAS_OP_N, m, n, k, &one, (const double*)A, lda, (const double*)B, ldb, &zero, (double*)C, ldc)); return true; }
-    case HYACIN_F32: { float one = 1.f, zero = 0.f; HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_R_32F, lda, B, CUDA_R_32F, ldb, &zero, C, CUDA_R_32F, ldc, CUBLAS_COMPUTE_32F_EMULATED_16BFX9, CUBLAS_GEMM_DEFAULT)); return true; }
+    case HYACIN_F32: {
+      // The emulated mode is the reference's (src/lra.cpp:92); the library refuses it for some leading dimensions and
+      // offsets (status NOT_SUPPORTED), where the reference carries on with an unwritten product.  Plain FP32 then.
+      float one = 1.f, zero = 0.f;
+      if (cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_R_32F, lda, B, CUDA_R_32F, ldb, &zero, C, CUDA_R_32F, ldc, CUBLAS_COMPUTE_32F_EMULATED_16BFX9, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS)
+        HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_R_32F, lda, B, CUDA_R_32F, ldb, &zero, C, CUDA_R_32F, ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+      return true;
+    }
     case HYACIN_F16: { __half one = __float2half(1.f), zero = __float2half(0.f); HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_R_16F, lda, B, CUDA_R_16F, ldb, &zero, C, CUDA_R_16F, ldc, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT)); return true; }
     case HYACIN_F64_COMPLEX: { cuDoubleComplex one = make_cuDoubleComplex(1., 0.), zero = make_cuDoubleComplex(0., 0.); HYB_LIB(cublasZgemm(b, opa, CUBLAS_OP_N, m, n, k, &one, (const cuDoubleComplex*)A, lda, (const cuDoubleComplex*)B, ldb, &zero, (cuDoubleComplex*)C, ldc)); return true; }
-    case HYACIN_F32_COMPLEX: { cuComplex one = make_cuComplex(1.f, 0.f), zero = make_cuComplex(0.f, 0.f); HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_C_32F, lda, B, CUDA_C_32F, ldb, &zero, C, CUDA_C_32F, ldc, CUBLAS_COMPUTE_32F_EMULATED_16BFX9, CUBLAS_GEMM_DEFAULT)); return true; }
+    case HYACIN_F32_COMPLEX: {
+      cuComplex one = make_cuComplex(1.f, 0.f), zero = make_cuComplex(0.f, 0.f);
+      if (cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_C_32F, lda, B, CUDA_C_32F, ldb, &zero, C, CUDA_C_32F, ldc, CUBLAS_COMPUTE_32F_EMULATED_16BFX9, CUBLAS_GEMM_DEFAULT) != CUBLAS_STATUS_SUCCESS)
+        HYB_LIB(cublasGemmEx(b, opa, CUBLAS_OP_N, m, n, k, &one, A, CUDA_C_32F, lda, B, CUDA_C_32F, ldb, &zero, C, CUDA_C_32F, ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+      return true;
+    }
     case HYACIN_F16_COMPLEX: {
       // The library has no complex-half GEMM: split into planes and use two real GEMMs per block of rows,
       //   [C_re | C_im] = A_re [B_re | B_im] + A_im [-B_im | B_re]

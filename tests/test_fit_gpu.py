@@ -378,6 +378,31 @@ def test_pivoted_cholesky_counts_a_last_single_column(hy, ref):
     assert _compare_cholesky(hy, ref, G, api.F64, n, n, 1e-12) == n
 
 
+@pytest.mark.parametrize("atype,op", [(api.F32, "T"), (api.F32_COMPLEX, "C")])
+def test_segmented_fit_in_single_precision_with_odd_leading_dimension(hy, atype, op):
+    """The stage products of single-precision input ask cuBLAS for its emulated FP32 mode, as the reference does
+    (src/lra.cpp:92,104).  The library refuses that mode for some leading dimensions and column offsets; the
+    reference then carries on with an unwritten product, this build repeats the product in plain FP32.  Checked
+    against the matrix itself: the basis reproduces it to the tolerance."""
+    torch = _torch()
+    rng = np.random.default_rng(537)
+    m, n, k, eps = 4000, 537, 74, 3e-5
+    r = 40
+    A = (rng.standard_normal((m, r)) * 10.0 ** (-6.0 * np.arange(r) / r)) @ rng.standard_normal((r, n)) / np.sqrt(m)
+    if atype & 1:
+        A = A + 1j * ((rng.standard_normal((m, r)) * 10.0 ** (-6.0 * np.arange(r) / r)) @ rng.standard_normal((r, n)) / np.sqrt(m))
+    from tests.helpers import NP_DTYPE
+    A = A.astype(NP_DTYPE[atype])
+    stored = np.ascontiguousarray(A.conj().T if op == "C" else A.T)           # stored N x M, lda = n
+    dA = to_device_colmajor(stored)
+    rank, S, V = _tsvd(hy, dA, op, m, n, k, n, eps, atype, segment_n=True)
+    assert 0 < rank <= k
+    s_true = np.linalg.svd(A.astype(np.complex128 if atype & 1 else np.float64), compute_uv=False)
+    assert np.max(np.abs(S.cpu().numpy()[:rank].astype(np.float64) - s_true[:rank])) <= 2e-4 * s_true[0]
+    assert _rel_error(hy, dA, op, m, n, n, rank, V, atype) <= 20 * eps
+    assert hy.status() == 0
+
+
 @pytest.mark.parametrize("op", ["N", "C"])
 def test_segmented_fit_on_complex_half_input(hy, ref, op):
     """hyacinTsvdFitSegmentN with complex-half storage: the stage products go through planar real GEMMs."""
