@@ -270,6 +270,7 @@ def _synthetic_gram(rng, n, gtype, decades):
     (api.F64, 1001, 600),           # odd n with 8-byte elements: padded pitch
     (api.F64, 1500, 1500),
     (api.F64_COMPLEX, 333, 333),
+    (api.F32_COMPLEX, 200, 120),
     (api.DD, 1024, 700),
     (api.DD_COMPLEX, 200, 200),
     (api.DD_COMPLEX, 1024, 300),
