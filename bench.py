@@ -108,18 +108,34 @@ def make_nccl_comm(torch, dist, rank, world):
 
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """nvidia-smi sampling every 100 ms in a child process.  Started before the warm-up (the tool needs some tenths of a
+    second before its first line); `mark()` opens the timed region and `stop()` closes it, and only samples whose own
+    timestamp lies inside the region are reported (all of them if the region was too short to catch one)."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.t0 = time.time()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
+    def mark(self):
+        self.t0 = time.time()
+
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def stop(self):
+        t1 = time.time()
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
             return out
@@ -130,24 +146,29 @@ class ClockSampler:
             self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in self.file.read().splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0])); mx.append(float(parts[1]))
+                rows.append((self._stamp(parts[0]), float(parts[1]), float(parts[2]), parts[4:8]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
+        os.unlink(self.file.name)
+        inside = [r for r in rows if r[0] is not None and self.t0 - 0.02 <= r[0] <= t1 + 0.02]
+        rows = inside or rows
+        reasons = set()
+        for _, _, _, flags in rows:
+            for name, val in zip(names, flags):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        os.unlink(self.file.name)
-        if sm:
-            out["sm_mhz"] = statistics.median(sm)
-            out["sm_max_mhz"] = max(mx)
-            out["samples"] = len(sm)
+        if rows:
+            out["sm_mhz"] = statistics.median(r[1] for r in rows)
+            out["sm_max_mhz"] = max(r[2] for r in rows)
+            out["samples"] = len(rows)
+            out["samples_inside_timed_region"] = len(inside)
         out["reasons"] = sorted(reasons)
         return out
 
@@ -366,20 +387,24 @@ def main():
 
     int8_peak = int8_gemm_peak(torch, 1.5) if (mine and rank == 0 and not args.complex and not args.no_peak) else None
     barrier()
+    clocks = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 0)):
         gram_step()
     barrier()
     if mine:
         h.launch_count(reset=True)
         h.profile_enable(True)
-    clocks = ClockSampler(local) if rank == 0 else None
+    torch.cuda.synchronize()
+    if clocks:
+        clocks.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         gtype, gbytes = gram_step()
     e1.record()
-    barrier()
+    torch.cuda.synchronize()
     clock_info = clocks.stop() if clocks else None
+    barrier()
     step_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     launches = h.launch_count() if mine else None
     prof = h.profile_read() if mine else None
@@ -562,13 +587,15 @@ def run_fit_config(args, torch, api, workloads, h, rank, world, barrier, max_ove
         def step():
             return h.interpolate_fit(eps, "T", m, n, k, stored, n, jp, V, n, global_m, atype)
 
+    clocks = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
     for _ in range(max(args.warmup, 0)):
         fit_rank = step()
     h.sync_timer(); barrier()
     if mine:
         h.launch_count(reset=True)
         h.profile_enable(True)
-    clocks = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))) if rank == 0 else None
+    if clocks:
+        clocks.mark()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         fit_rank = step()
