@@ -363,7 +363,19 @@ extern "C" int32_t hyacinXGevd(const hyacinHandle_t* handle, double eps, int32_t
   const int svd_rank = *r_host;
   rank = std::min(rank, svd_rank);
   pool_free(handle, sigma); pool_free(handle, suffix);
-  convert_copy(stream, 'N', N, rank, lt, U, N, Atype, X, ldx);
+  // Same storage and library type: the copy goes through cuBLAS geam as in the reference (src/matcopy.cu:100-108).  For
+  // complex data that is a multiplication by (1, 0), which turns an imaginary part of -0 into +0: part of the bits of V.
+  if (lt == Atype && rank > 0) {
+    cublasHandle_t b = handle->cublasHandle;
+    switch (int(lt)) {
+      case HYACIN_F64: { const double one = 1., zero = 0.; HYB_LIB(cublasDgeam(b, CUBLAS_OP_N, CUBLAS_OP_N, N, rank, &one, (const double*)U, N, &zero, (const double*)X, ldx, (double*)X, ldx)); break; }
+      case HYACIN_F32: { const float one = 1.f, zero = 0.f; HYB_LIB(cublasSgeam(b, CUBLAS_OP_N, CUBLAS_OP_N, N, rank, &one, (const float*)U, N, &zero, (const float*)X, ldx, (float*)X, ldx)); break; }
+      case HYACIN_F64_COMPLEX: { const cuDoubleComplex one = make_cuDoubleComplex(1., 0.), zero = make_cuDoubleComplex(0., 0.);
+        HYB_LIB(cublasZgeam(b, CUBLAS_OP_N, CUBLAS_OP_N, N, rank, &one, (const cuDoubleComplex*)U, N, &zero, (const cuDoubleComplex*)X, ldx, (cuDoubleComplex*)X, ldx)); break; }
+      default: { const cuComplex one = make_cuComplex(1.f, 0.f), zero = make_cuComplex(0.f, 0.f);
+        HYB_LIB(cublasCgeam(b, CUBLAS_OP_N, CUBLAS_OP_N, N, rank, &one, (const cuComplex*)U, N, &zero, (const cuComplex*)X, ldx, (cuComplex*)X, ldx)); break; }
+    }
+  } else convert_copy(stream, 'N', N, rank, lt, U, N, Atype, X, ldx);
   pool_free(handle, U);
   if (handle->logger) {
     static const char* names[4] = {"FP64", "FP64-COMPLEX", "FP32", "FP32-COMPLEX"};

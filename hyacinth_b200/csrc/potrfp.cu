@@ -159,21 +159,22 @@ constexpr int kMaxStages = 4;
 // The best remaining diagonal entry seen so far, the remaining trace, and whether a bounded wait expired.
 // key: place of the entry in the order in which the reference's reduction meets the candidates -- among equal
 // values the smallest key wins.
-template <typename R> struct Partial { R val; double trace; int pos; int key; int flag; int pad; };
+// abs_sum: sum of the magnitudes behind `trace`; it bounds how far two summation orders of the trace can differ.
+template <typename R> struct Partial { R val; double trace; double abs_sum; int pos; int key; int flag; int pad; };
 
 template <typename R> __device__ __forceinline__ Partial<R> empty_partial() {
-  Partial<R> p; p.val = Real<R>::zero(); p.trace = 0.; p.pos = -1; p.key = 0x7fffffff; p.flag = 0; p.pad = 0; return p;
+  Partial<R> p; p.val = Real<R>::zero(); p.trace = 0.; p.abs_sum = 0.; p.pos = -1; p.key = 0x7fffffff; p.flag = 0; p.pad = 0; return p;
 }
 // A candidate replaces the current best only if it is larger; the search starts from zero, so entries <= 0 are
 // never chosen (src/hyacin_potrfp.cu:111-116).
 template <typename R> __device__ __forceinline__ void merge_partial(Partial<R>& a, const Partial<R>& b) {
-  a.trace += b.trace; a.flag |= b.flag;
+  a.trace += b.trace; a.abs_sum += b.abs_sum; a.flag |= b.flag;
   if (b.pos < 0) return;
   const bool take = a.pos < 0 || Real<R>::less(a.val, b.val) || (!Real<R>::less(b.val, a.val) && b.key < a.key);
   if (take) { a.val = b.val; a.pos = b.pos; a.key = b.key; }
 }
 template <typename R> __device__ __forceinline__ void offer(Partial<R>& a, R d, int pos, int key) {
-  a.trace += Real<R>::to_double(d);
+  a.trace += Real<R>::to_double(d); a.abs_sum += fabs(Real<R>::to_double(d));
   if (!Real<R>::less(Real<R>::zero(), d)) return;
   if (a.pos < 0 || Real<R>::less(a.val, d) || (!Real<R>::less(d, a.val) && key < a.key)) { a.val = d; a.pos = pos; a.key = key; }
 }
@@ -181,6 +182,7 @@ template <typename R> __device__ __forceinline__ void warp_merge_partial(Partial
   for (int o = 16; o > 0; o >>= 1) {
     Partial<R> other;
     other.val = shfl_down_real(mine.val, o); other.trace = __shfl_down_sync(0xffffffffu, mine.trace, o);
+    other.abs_sum = __shfl_down_sync(0xffffffffu, mine.abs_sum, o);
     other.pos = __shfl_down_sync(0xffffffffu, mine.pos, o); other.key = __shfl_down_sync(0xffffffffu, mine.key, o);
     other.flag = __shfl_down_sync(0xffffffffu, mine.flag, o); other.pad = 0;
     merge_partial(mine, other);
@@ -208,12 +210,12 @@ __device__ __forceinline__ double ldcg_real(const double* p) { return __ldcg(p);
 __device__ __forceinline__ DD ldcg_real(const DD* p) { return DD{__ldcg(&p->x), __ldcg(&p->y)}; }
 
 template <typename R> __device__ __forceinline__ void publish(Partial<R>* slot, const Partial<R>& p) {
-  slot->val = p.val; slot->trace = p.trace; slot->pos = p.pos; slot->key = p.key; slot->flag = p.flag;
+  slot->val = p.val; slot->trace = p.trace; slot->abs_sum = p.abs_sum; slot->pos = p.pos; slot->key = p.key; slot->flag = p.flag;
 }
 template <typename R> __device__ __forceinline__ Partial<R> fetch(const Partial<R>* slot) {
   // L2 loads: these words are rewritten by other blocks every second step
   Partial<R> p = empty_partial<R>();
-  p.val = ldcg_real(&slot->val); p.trace = __ldcg(&slot->trace); p.pos = __ldcg(&slot->pos); p.key = __ldcg(&slot->key); p.flag = __ldcg(&slot->flag);
+  p.val = ldcg_real(&slot->val); p.trace = __ldcg(&slot->trace); p.abs_sum = __ldcg(&slot->abs_sum); p.pos = __ldcg(&slot->pos); p.key = __ldcg(&slot->key); p.flag = __ldcg(&slot->flag);
   return p;
 }
 
@@ -280,6 +282,57 @@ template <int MPG> __device__ __forceinline__ int tree_column_of_lane(int lane) 
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------------
+// The remaining trace summed in the order of the reference's reduction (src/hyacin_potrfp.cu:128-132, 243-261), for the
+// stop comparison when it falls within rounding distance (exactly rank-deficient matrices: the remaining diagonal is
+// rounding noise) and for the initial trace behind the threshold.  Candidate number th sits in thread th % 128 of block
+// th / 128 of the reference; its thread 0 first takes the column that was swapped into the pivot's old place (relative
+// position j_rel, if j_rel > 0), then its own; a block sums its 128 threads by the shuffle tree and its four warps left to
+// right; thread t of block 0 adds the sums of blocks t + 1, t + 129, ... to its own start value (thread 0: its block's sum,
+// the others: zero) and the 128 threads are summed by the same tree.  Candidate th is the column at position
+// base + th + 1, or base + th + 2 from the swapped one on.  Holds while every reference thread has at most one candidate:
+// n <= kExactColumns.  Called by all threads of the block; the result is the same in every block.
+constexpr int kExactBlocks = 148;
+constexpr int kExactColumns = kExactBlocks * 128;
+template <typename R>
+__device__ __forceinline__ double reference_order_trace(const R* D, const uint16_t* perm, int base, int j_rel, int count,
+                                                        double* s_agg, double* s_out, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const int nb = count > 0 ? (count + 127) >> 7 : 1;
+  for (int b = warp; b < nb; b += kThreads / 32) {
+    double w4[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int th = 128 * b + 32 * q + lane;
+      double x = 0.0;
+      if (th < count) {
+        const int l = (j_rel > 0 && th + 1 >= j_rel) ? th + 2 : th + 1;
+        x = Real<R>::to_double(ldcg_real(&D[perm[base + l]]));
+      }
+      if (th == 0 && j_rel > 0) x = Real<R>::to_double(ldcg_real(&D[perm[base + j_rel]])) + x;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) x += __shfl_down_sync(0xffffffffu, x, o);
+      w4[q] = x;
+    }
+    if (lane == 0) s_agg[b] = ((w4[0] + w4[1]) + w4[2]) + w4[3];
+  }
+  __syncthreads();
+  if (warp == 0) {
+    double w4[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int t = 32 * q + lane;
+      double u = t == 0 ? s_agg[0] : 0.0;
+      for (int i = t + 1; i < nb; i += 128) u += s_agg[i];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) u += __shfl_down_sync(0xffffffffu, u, o);
+      w4[q] = u;
+    }
+    if (lane == 0) *s_out = ((w4[0] + w4[1]) + w4[2]) + w4[3];
+  }
+  __syncthreads();
+  return *s_out;
+}
+
 template <typename R, bool CPLX>
 __global__ void __launch_bounds__(kThreads, 1)
 potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restrict__ G, int64_t ldg, Elem<R, CPLX>* __restrict__ Rc, int64_t ldc,
@@ -295,6 +348,7 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
   __shared__ E s_part[kGroups][32];                 // tree result of each group of 32 chains, per column of the pass
   __shared__ P s_red[2][kThreads / 32];             // by step parity: a warp may still read one step's while another writes the next's
   __shared__ R s_rinv;
+  __shared__ double s_agg[kExactBlocks], s_exact;
   __shared__ uint32_t s_abort, s_issued;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblocks = gridDim.x;
@@ -334,8 +388,13 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
 
   const int iter_n = cap >= n ? 1 : n - cap;         // columns left at which the rank cap stops the loop
   double threshold = 0.;
-  int k = 0, rank = 0;
+  int k = 0, rank = 0, j_last = 0;
   for (;; ++k) {
+    // The remaining diagonal lives in two arrays that alternate by step: step k reads D_now and writes D_next, so a block
+    // that still sums D_now for its stop decision (reference_order_trace) is not overtaken by the writes of step k; the
+    // grid barrier at the end of step k separates those reads from the writes of step k + 1 into the same array.
+    const R* D_now = D + size_t(k & 1) * n;
+    R* D_next = D + size_t((k + 1) & 1) * n;
     // ---- read and reduce the records of all blocks in the same order: same pivot everywhere ----
     P best;
     {
@@ -352,10 +411,15 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
     if (best.flag) { rank = -1; break; }
     if (k == 0) {
       if (!have) { rank = 0; break; }
-      threshold = eps_sq * best.trace;
+      threshold = eps_sq * (n <= kExactColumns ? reference_order_trace<R>(D_now, perm, -1, 0, n, s_agg, &s_exact, tid) : best.trace);
     } else {
       const int remaining = n - k;
-      if (!(have && threshold < best.trace) || remaining <= iter_n) {
+      double trace = best.trace;
+      // this build's sum and the reference's differ by at most a few n ulps of the summed magnitudes: only a comparison
+      // closer than that needs the reference's own order
+      if (n <= kExactColumns && have && remaining > iter_n && fabs(trace - threshold) <= 1.8e-15 * double(n) * best.abs_sum)
+        trace = reference_order_trace<R>(D_now, perm, k - 1, j_last, remaining - (j_last > 0 ? 1 : 0), s_agg, &s_exact, tid);
+      if (!(have && threshold < trace) || remaining <= iter_n) {
         rank = k + (remaining == 1 ? 1 : 0);
         if (remaining == 1 && blockIdx.x == 0 && tid == 0) {
           // a last single column is counted whatever its diagonal entry is; its row holds the root alone
@@ -370,6 +434,7 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
     // is updated at the END of the step (the order of columns that are never chosen is part of the result, so the
     // swap happens only for steps that run); until then everybody reads it through column_at().
     const int q_pivot = best.pos, j = q_pivot - k;   // position of the pivot before the swap, and relative to k
+    j_last = j;
     const int pc = perm[q_pivot], front = perm[k];
     auto column_at = [&](int q) -> int { return q == q_pivot ? front : int(perm[q]); };
 
@@ -428,7 +493,7 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
         }
         // what the end of the pass needs from global memory is requested now
         R dv = T::zero(); int my_col = 0;
-        if (tid < cwr) { my_col = column_at(r0 + tid); dv = ldcg_real(&D[my_col]); }
+        if (tid < cwr) { my_col = column_at(r0 + tid); dv = ldcg_real(&D_now[my_col]); }
 #define HYB_STAGES(N) case N: consume_stages<R, CPLX, N>(acc, ring, shape, full_bar, empty_bar, consumed, dead, S, nstages, k, chain, c_first, lane, &s_abort, status); break;
         if constexpr (kMaxPerGroup == 8) {
           switch (my_cols) { HYB_STAGES(0) HYB_STAGES(1) HYB_STAGES(2) HYB_STAGES(3) HYB_STAGES(4) HYB_STAGES(5) HYB_STAGES(6) HYB_STAGES(7) default: HYB_STAGES(8) }
@@ -451,7 +516,7 @@ potrfp_chain_kernel(double eps_sq, int n, int cap, const Elem<R, CPLX>* __restri
           if (k > 0) { w = O::add(w, s_part[1][tid]); w = O::add(w, s_part[2][tid]); w = O::add(w, s_part[3][tid]); }
           const E out = O::finish(dv, s_rinv, w);
           Rc[size_t(my_col) * ldc + k] = out;
-          D[my_col] = dv;
+          D_next[my_col] = dv;
           ptx::fence_proxy_async_global();              // later steps read the factor through the async proxy
           // place of this column in the reference's scan of the remaining diagonal: the column that moved from
           // position k to the pivot's old place comes first, then the others by position (src/hyacin_potrfp.cu:243-252)
@@ -531,7 +596,7 @@ int run_potrfp(const hyacinHandle_t* handle, double eps, int cap, int n, const v
   // one block per SM at most (the kernel is launched cooperatively), at least four columns per block
   const int grid = std::max(1, std::min(std::max(handle->DeviceSMs, 1), (n + 3) / 4));
   R* D = nullptr; P* partials = nullptr;
-  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&D), size_t(n) * sizeof(R), handle->mempool, stream));
+  HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&D), size_t(2) * n * sizeof(R), handle->mempool, stream));      // two arrays, by step parity
   HYB_CUDA(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&partials), size_t(2) * grid * sizeof(P), handle->mempool, stream));
   int32_t* rank_host = static_cast<int32_t*>(handle->pinnedWorkspace);
   *rank_host = 0;

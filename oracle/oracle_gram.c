@@ -352,7 +352,8 @@ void orc_dequantize(int32_t N, int32_t order, const uint64_t* C, const int32_t* 
  *   - entry r = w / sqrt(d) as a product with 1 / sqrt(d), diagonal d -= |r|^2 by fused multiply-adds (:172-176);
  *   - pivot = largest remaining diagonal entry, ties to the candidate the reference's reduction meets first (:243-261);
  *   - stop when the remaining trace <= eps^2 * initial trace, or N - K columns are left; a single remaining column is
- *     always counted (:262-269).
+ *     always counted (:262-269); both traces are summed in the order of the reference's reduction, so the comparison
+ *     has the reference's bits even when it is taken on rounding noise (exactly rank-deficient matrices).
  * Only the double formats are restated: their arithmetic is explicit fused multiply-adds.  The double-double formats
  * depend on which products the device compiler contracts and are checked against the reference library on the GPU.
  * G: n x n column-major (2 doubles per entry if cplx).  R: rows x n column-major BY POSITION, R[k + x ldr] for k <= x,
@@ -373,6 +374,28 @@ static double tree128(const double* x) {
   return ((g[0] + g[1]) + g[2]) + g[3];
 }
 
+/* Remaining trace in the order of the reference's reduction (src/hyacin_potrfp.cu:243-261, 128-132): candidate number th sits
+ * in thread th % 128 of block th / 128; thread 0 of block 0 first takes the one extra value `special` (the column swapped
+ * into the pivot's old place), then its own; a block sums its 128 threads by the shuffle tree and its four warps left to
+ * right; thread t of block 0 then adds the sums of blocks t + 1, t + 129, ... to its own (thread 0: its block's sum, the
+ * others: zero) and the 128 threads are summed by the same tree.  Valid while every thread holds at most one candidate
+ * (n <= 148 * 128 on a B200 whatever the occupancy of the reference's kernel). */
+static double trace_in_reference_order(const double* d, int count, int have_special, double special) {
+  const int nb = count > 0 ? (count + 127) / 128 : 1;
+  double* agg = (double*)malloc((size_t)nb * sizeof(double));
+  for (int b = 0; b < nb; ++b) {
+    double x[128];
+    for (int t = 0; t < 128; ++t) { const int th = 128 * b + t; x[t] = th < count ? d[th] : 0.0; }
+    if (b == 0 && have_special) x[0] = (0.0 + special) + x[0];
+    agg[b] = tree128(x);
+  }
+  double u[128];
+  for (int t = 0; t < 128; ++t) { u[t] = t == 0 ? agg[0] : 0.0; for (int i = t + 1; i < nb; i += 128) u[t] += agg[i]; }
+  const double out = tree128(u);
+  free(agg);
+  return out;
+}
+
 int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const double* G, int64_t ldg, int32_t* jpiv, double* R, int64_t ldr) {
   const int w = cplx ? 2 : 1;
   if (n <= 0 || cap <= 0) return 0;
@@ -386,11 +409,13 @@ int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const d
   const int iter_n = cap >= n ? 1 : n - cap;
   /* first candidates: position i is the reference's candidate number i */
   double trace = 0.0, best = 0.0; int best_pos = -1, best_key = INT_MAX;
+  double* cand = (double*)malloc((size_t)n * sizeof(double));      /* remaining diagonal entries by candidate number */
   for (int i = 0; i < n; ++i) {
-    perm[i] = i; D[i] = G[((int64_t)i + (int64_t)i * ldg) * w]; trace += D[i];
+    perm[i] = i; D[i] = G[((int64_t)i + (int64_t)i * ldg) * w]; cand[i] = D[i];
     int key = chol_key(i, 0);
     if (D[i] > 0.0 && (best_pos < 0 || best < D[i] || (best == D[i] && key < best_key))) { best = D[i]; best_pos = i; best_key = key; }
   }
+  trace = trace_in_reference_order(cand, n, 0, 0.0);
   double threshold = 0.0; int rank = 0, k = 0;
   for (;; ++k) {
     const int have = best_pos >= 0;
@@ -406,7 +431,8 @@ int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const d
     const int q = best_pos, j = q - k, pc = perm[q], front = perm[k];
     const double root = sqrt(best), rinv = 1.0 / root;
     F[((size_t)pc * rows + k) * w] = root;
-    trace = 0.0; best = 0.0; best_pos = -1; best_key = INT_MAX;
+    best = 0.0; best_pos = -1; best_key = INT_MAX;
+    double special = 0.0; int count = 0;
     for (int p = k + 1; p < n; ++p) {
       const int col = p == q ? front : perm[p];
       const double* fc = F + (size_t)col * rows * w; const double* fp = F + (size_t)pc * rows * w;
@@ -426,13 +452,16 @@ int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const d
       double d = D[col];
       if (cplx) { const double rr = rinv * wr, ri = -rinv * wi; d = fma(-rr, rr, fma(-ri, ri, d)); F[((size_t)col * rows + k) * 2] = rr; F[((size_t)col * rows + k) * 2 + 1] = ri; }
       else { const double rc = rinv * wr; d = fma(-rc, rc, d); F[(size_t)col * rows + k] = rc; }
-      D[col] = d; trace += d;
+      D[col] = d;
       const int l = p - k;
+      if (j > 0 && l == j) special = d; else { cand[j > 0 ? l - (l > j ? 1 : 0) - 1 : l - 1] = d; ++count; }
       const int key = (j > 0 && l == j) ? chol_key(0, 0) : (j > 0 ? chol_key(l - (l > j ? 1 : 0) - 1, 1) : chol_key(l - 1, 1));
       if (d > 0.0 && (best_pos < 0 || best < d || (best == d && key < best_key))) { best = d; best_pos = p; best_key = key; }
     }
+    trace = trace_in_reference_order(cand, count, j > 0, special);
     perm[q] = front; perm[k] = pc;
   }
+  free(cand);
   for (int x = 0; x < n; ++x) {
     jpiv[x] = perm[x] + 1;
     for (int kk = 0; kk < rank && kk < rows; ++kk)

@@ -370,6 +370,32 @@ def test_pivoted_cholesky_matches_cpu_oracle(hy, cplx, n, cap, eps):
     assert hy.status() == 0
 
 
+def test_exactly_rank_deficient_inputs_give_the_reference_bits(hy, ref):
+    """Inputs of exact rank one to three: once the rank is used up the remaining diagonal of the Gram matrix is rounding
+    noise, and whether the Cholesky takes one more (noise) row depends on the last bits of the remaining trace, i.e. on
+    the order in which the reference sums it.  Rank, S and every bit of V must still agree."""
+    torch = _torch()
+    gen = torch.Generator(device="cuda"); gen.manual_seed(2024)
+    rng = np.random.default_rng(2024)
+    checked = 0
+    for case in range(240):
+        cplx = case % 3 != 0
+        m, n, r = int(rng.integers(50, 3000)), int(rng.integers(2, 120)), int(rng.integers(1, 4))
+        dt = torch.complex128 if cplx else torch.float64
+        A = torch.randn((m, r), generator=gen, device="cuda", dtype=dt) @ torch.randn((r, n), generator=gen, device="cuda", dtype=dt)
+        dA = A.transpose(0, 1).contiguous()
+        atype = api.F64_COMPLEX if cplx else api.F64
+        eps = float(10.0 ** rng.uniform(-11, -6))
+        a = _tsvd(hy, dA, "N", m, n, n, m, eps, atype)
+        b = _tsvd(ref, dA, "N", m, n, n, m, eps, atype)
+        assert a[0] == b[0] > 0, (case, a[0], b[0])
+        rank = a[0]
+        assert torch.equal(a[1][:rank], b[1][:rank]), f"case {case}: singular values differ"
+        assert torch.equal(a[2][:rank].view(torch.uint8), b[2][:rank].view(torch.uint8)), f"case {case}: basis differs (m={m}, n={n}, rank {r}, complex={cplx})"
+        checked += 1
+    assert checked == 240 and hy.status() == 0
+
+
 def test_pivoted_cholesky_counts_a_last_single_column(hy, ref):
     """With K = N the loop stops when one column is left and counts it (src/hyacin_potrfp.cu:264,269 of the
     reference): a full-rank matrix gives rank N and a complete factor."""
