@@ -116,22 +116,35 @@ bool stage_gemm(const hyacinHandle_t* h, hyacinPrecision_t t, char op, int m, in
       return true;
     }
     case HYACIN_F16_COMPLEX: {
-      // The library has no complex-half GEMM: split into planes and use two real GEMMs per block of rows,
-      //   [C_re | C_im] = A_re [B_re | B_im] + A_im [-B_im | B_re]
-      // (the arrangement of src/matmul_fp16_complex.cu; here with FP32 accumulation and any op(A) handled by
-      // the splitting kernel instead of one routine per transposition).
-      const int block = 8192;
-      __half* bp = pool_alloc<__half>(h, size_t(3) * k * n);
-      __half* ap = pool_alloc<__half>(h, size_t(2) * block * k);
-      __half* cp = pool_alloc<__half>(h, size_t(2) * block * n);
-      split_complex_half_b(h->cudaStream, k, n, B, ldb, bp, k);
-      const float one = 1.f, zero = 0.f;
+      // The library has no complex-half GEMM: split into planes and use two real GEMMs per block of 8192 rows,
+      //   [C_re | C_im] = A_re [B_re | B_im] + A_im [-B_im | B_re].
+      // Operand layouts, padding of K to a multiple of 8, leading dimensions and the half-precision compute type are
+      // those of src/matmul_fp16_complex.cu (planes of a stored-transposed A stay K-major and enter with op T), so that
+      // cuBLAS is asked for the very same products and returns the same bits.
+      const int block = 8192, ak = (k + 7) & ~7;
+      const bool stored_t = op == 'T' || op == 'C';
+      const size_t plane_a = size_t(block) * ak, plane_b = size_t(ak) * n, plane_c = size_t(block) * n;
+      __half* bp = pool_alloc<__half>(h, 3 * plane_b);
+      __half* ap = pool_alloc<__half>(h, 2 * plane_a);
+      __half* cp = pool_alloc<__half>(h, 2 * plane_c);
+      HYB_CUDA(cudaMemsetAsync(bp, 0, 3 * plane_b * sizeof(__half), h->cudaStream));       // the padding rows K .. ak - 1 stay zero
+      HYB_CUDA(cudaMemsetAsync(ap, 0, 2 * plane_a * sizeof(__half), h->cudaStream));
+      split_complex_half_b(h->cudaStream, k, n, B, ldb, bp, ak);
+      const __half one = __float2half(1.f), zero = __float2half(0.f);
       for (int i = 0; i < m; i += block) {
         const int rows = std::min(block, m - i);
-        split_complex_half(h->cudaStream, op, i, rows, k, A, lda, ap, ap + size_t(block) * k, rows);
-        HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, k, &one, ap, CUDA_R_16F, rows, bp + size_t(k) * n, CUDA_R_16F, k, &zero, cp, CUDA_R_16F, rows, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
-        HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, k, &one, ap + size_t(block) * k, CUDA_R_16F, rows, bp, CUDA_R_16F, k, &one, cp, CUDA_R_16F, rows, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
-        merge_complex_half(h->cudaStream, rows, n, cp, cp + size_t(rows) * n, rows, static_cast<char*>(C) + size_t(i) * 4, ldc);
+        if (stored_t) {
+          // stored K x M: columns i .. i + rows - 1, planes [kk + r ak]
+          split_complex_half_stored(h->cudaStream, op == 'C', k, rows, static_cast<const char*>(A) + size_t(i) * lda * 4, lda, ap, ap + plane_a, ak);
+          HYB_LIB(cublasGemmEx(b, CUBLAS_OP_T, CUBLAS_OP_N, rows, 2 * n, ak, &one, ap, CUDA_R_16F, ak, bp + plane_b, CUDA_R_16F, ak, &zero, cp, CUDA_R_16F, block, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT));
+          HYB_LIB(cublasGemmEx(b, CUBLAS_OP_T, CUBLAS_OP_N, rows, 2 * n, ak, &one, ap + plane_a, CUDA_R_16F, ak, bp, CUDA_R_16F, ak, &one, cp, CUDA_R_16F, block, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT));
+        } else {
+          // stored M x K: rows i .. i + rows - 1, planes [r + kk block]
+          split_complex_half_stored(h->cudaStream, false, rows, k, static_cast<const char*>(A) + size_t(i) * 4, lda, ap, ap + plane_a, block);
+          HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, ak, &one, ap, CUDA_R_16F, block, bp + plane_b, CUDA_R_16F, ak, &zero, cp, CUDA_R_16F, block, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT));
+          HYB_LIB(cublasGemmEx(b, CUBLAS_OP_N, CUBLAS_OP_N, rows, 2 * n, ak, &one, ap + plane_a, CUDA_R_16F, block, bp, CUDA_R_16F, ak, &one, cp, CUDA_R_16F, block, CUBLAS_COMPUTE_16F, CUBLAS_GEMM_DEFAULT));
+        }
+        merge_complex_half(h->cudaStream, rows, n, cp, cp + plane_c, block, static_cast<char*>(C) + size_t(i) * 4, ldc);
       }
       pool_free(h, bp); pool_free(h, ap); pool_free(h, cp);
       return true;

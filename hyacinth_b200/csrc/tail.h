@@ -42,6 +42,7 @@ void interp_scatter(cudaStream_t stream, int n, int rank, const int32_t* jpiv, h
 // split_b: three panels of cols columns each, (-im, re, im), so that [re | im] and [-im | re] are contiguous
 //        (rows x 2 cols) operands.  merge: dst complex <- (re, im).
 void split_complex_half(cudaStream_t stream, char op, int64_t row0, int rows, int cols, const void* src, int64_t lds, void* re, void* im, int64_t ld);
+void split_complex_half_stored(cudaStream_t stream, bool conj, int rows, int cols, const void* src, int64_t lds, void* re, void* im, int64_t ld);
 void split_complex_half_b(cudaStream_t stream, int rows, int cols, const void* src, int64_t lds, void* panels, int64_t ld);
 void merge_complex_half(cudaStream_t stream, int rows, int cols, const void* re, const void* im, int64_t ld, void* dst, int64_t ldd);
 

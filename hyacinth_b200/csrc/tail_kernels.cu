@@ -171,7 +171,7 @@ __global__ void split_complex_half_kernel(int trans, int conj, int64_t row0, int
   if (!trans) {
     for (int j = threadIdx.y; j < 32; j += blockDim.y) {
       const int r = r0 + threadIdx.x, c = c0 + j;
-      if (r < rows && c < cols) { const __half2 v = src[row0 + r + int64_t(c) * lds]; re[r + int64_t(c) * ld] = v.x; im[r + int64_t(c) * ld] = v.y; }
+      if (r < rows && c < cols) { const __half2 v = src[row0 + r + int64_t(c) * lds]; re[r + int64_t(c) * ld] = v.x; im[r + int64_t(c) * ld] = conj ? __hneg(v.y) : v.y; }
     }
     return;
   }
@@ -313,6 +313,14 @@ void split_complex_half(cudaStream_t stream, char op, int64_t row0, int rows, in
   const int trans = op == 'T' || op == 'C';
   split_complex_half_kernel<<<dim3((rows + 31) / 32, (cols + 31) / 32), dim3(32, 8), 0, stream>>>(
       trans, op == 'C', row0, rows, cols, static_cast<const __half2*>(src), lds, static_cast<__half*>(re), static_cast<__half*>(im), ld);
+  HYB_CUDA(cudaGetLastError());
+}
+// The planes in the stored layout (no transposition): element (r, c) of the stored matrix to re / im [r + c ld], the
+// imaginary plane negated when conj is set.
+void split_complex_half_stored(cudaStream_t stream, bool conj, int rows, int cols, const void* src, int64_t lds, void* re, void* im, int64_t ld) {
+  if (rows <= 0 || cols <= 0) return;
+  split_complex_half_kernel<<<dim3((rows + 31) / 32, (cols + 31) / 32), dim3(32, 8), 0, stream>>>(
+      0, conj ? 1 : 0, 0, rows, cols, static_cast<const __half2*>(src), lds, static_cast<__half*>(re), static_cast<__half*>(im), ld);
   HYB_CUDA(cudaGetLastError());
 }
 void split_complex_half_b(cudaStream_t stream, int rows, int cols, const void* src, int64_t lds, void* panels, int64_t ld) {
