@@ -221,6 +221,15 @@ def pivoted_cholesky(G: np.ndarray, cap: int, eps: float):
     return int(rank), jpiv, R
 
 
+def trace_in_reference_order(d: np.ndarray, special=None) -> float:
+    """Sum of the remaining diagonal entries `d` (by candidate number) in the order of the reference's reduction
+    (src/hyacin_potrfp.cu:128-132, 243-261); `special` is the extra value its first thread takes before its own."""
+    d = np.ascontiguousarray(d, dtype=np.float64)
+    fn = lib().orc_trace_in_reference_order
+    fn.restype = ctypes.c_double
+    return float(fn(_ptr(d), ctypes.c_int32(d.size), ctypes.c_int32(0 if special is None else 1), ctypes.c_double(0.0 if special is None else special)))
+
+
 def limbs_to_int(words, order: int) -> int:
     """Value of one packed entry given its `order` 63-bit limbs (last limb signed)."""
     v = 0

@@ -396,6 +396,11 @@ static double trace_in_reference_order(const double* d, int count, int have_spec
   return out;
 }
 
+/* exported for the tests of the summation order itself */
+double orc_trace_in_reference_order(const double* d, int32_t count, int32_t have_special, double special) {
+  return trace_in_reference_order(d, count, have_special, special);
+}
+
 int32_t orc_potrfp_f64(int32_t n, int32_t cap, double eps, int32_t cplx, const double* G, int64_t ldg, int32_t* jpiv, double* R, int64_t ldr) {
   const int w = cplx ? 2 : 1;
   if (n <= 0 || cap <= 0) return 0;

@@ -114,3 +114,48 @@ def test_handle_layout_matches_the_c_header(tmp_path):
         subprocess.check_call(["gcc", "-I", inc, "-I", "/usr/local/cuda/include", str(src), "-o", str(exe)])
         got = [int(v) for v in subprocess.check_output([str(exe)], text=True).split()]
         assert got == want, inc
+
+
+def test_trace_summation_order_of_the_cholesky_stop_rule():
+    """The stop rule of the pivoted Cholesky compares rounding noise for exactly rank-deficient matrices, so the order
+    of the trace sum is part of the result.  A pure-Python statement of the reference's reduction (candidate th in
+    thread th % 128 of block th // 128; its first thread takes one extra value first; shuffle tree over 32 lanes,
+    four warps left to right; thread t of block 0 then walks blocks t + 1, t + 129, ...; same tree again) against the
+    C oracle, on values whose sum depends on the order."""
+    def tree128(x):
+        g = []
+        for w in range(4):
+            v = list(x[32 * w:32 * w + 32])
+            o = 1
+            while o < 32:
+                for i in range(0, 32 - o, 2 * o):
+                    v[i] = v[i] + v[i + o]
+                o *= 2
+            g.append(v[0])
+        return ((g[0] + g[1]) + g[2]) + g[3]
+
+    def reference_sum(d, special):
+        count = len(d)
+        nb = max(1, -(-count // 128))
+        agg = []
+        for b in range(nb):
+            x = [float(d[128 * b + t]) if 128 * b + t < count else 0.0 for t in range(128)]
+            if b == 0 and special is not None:
+                x[0] = (0.0 + special) + x[0]
+            agg.append(tree128(x))
+        u = []
+        for t in range(128):
+            acc = agg[0] if t == 0 else 0.0
+            for i in range(t + 1, nb, 128):
+                acc += agg[i]
+            u.append(acc)
+        return tree128(u)
+
+    rng = np.random.default_rng(5)
+    differs = 0
+    for count, special in [(1, None), (5, 0.3), (127, None), (128, 1e-3), (129, None), (1000, -2.5e-9), (4095, 7.0), (18943, None), (0, 1.5)]:
+        d = rng.standard_normal(count) * 10.0 ** rng.uniform(-12, 0, count)
+        want = reference_sum(d, special)
+        assert O.trace_in_reference_order(d, special) == want
+        differs += want != float(np.sum(d) + (special or 0.0))
+    assert differs > 0            # the order does matter for such values
