@@ -370,6 +370,33 @@ def test_pivoted_cholesky_matches_cpu_oracle(hy, cplx, n, cap, eps):
     assert hy.status() == 0
 
 
+@pytest.mark.parametrize("cplx,n,r", [(False, 300, 7), (True, 200, 3), (False, 1000, 130), (True, 64, 1)])
+def test_pivoted_cholesky_of_a_rank_deficient_gram_matches_cpu_oracle(hy, cplx, n, r):
+    """G = X X^H with r < n columns in X: after r steps the remaining diagonal is rounding noise of both signs and the
+    stop comparison is taken on it.  The kernel and the CPU restatement (which sums the trace in the reference's order)
+    must take the same decisions: rank, pivots and every bit of the factor equal."""
+    torch = _torch()
+    from oracle import oracle as O
+    rng = np.random.default_rng(7000 + n)
+    X = rng.standard_normal((n, r)) + (1j * rng.standard_normal((n, r)) if cplx else 0)
+    G = X @ X.conj().T
+    G = 0.5 * (G + G.conj().T)
+    gtype = api.F64_COMPLEX if cplx else api.F64
+    dG = torch.from_numpy(np.ascontiguousarray(G.T)).cuda()
+    for eps in (1e-7, 1e-14):
+        want_rank, want_jp, want_R = O.pivoted_cholesky(G, n, eps)
+        jp = torch.zeros(n, dtype=torch.int32, device="cuda")
+        R = torch.zeros((n, n), dtype=dG.dtype, device="cuda")
+        rank = hy.pivoted_cholesky(eps, n, n, gtype, dG, n, jp, R, n)
+        torch.cuda.synchronize()
+        assert rank == want_rank, (eps, rank, want_rank)
+        np.testing.assert_array_equal(jp.cpu().numpy(), want_jp)
+        rows = min(rank, n)
+        got = np.ascontiguousarray(R.cpu().numpy().T[:rows])
+        np.testing.assert_array_equal(got.view(np.uint8), np.ascontiguousarray(want_R[:rows]).view(np.uint8))
+    assert hy.status() == 0
+
+
 def test_exactly_rank_deficient_inputs_give_the_reference_bits(hy, ref):
     """Inputs of exact rank one to three: once the rank is used up the remaining diagonal of the Gram matrix is rounding
     noise, and whether the Cholesky takes one more (noise) row depends on the last bits of the remaining trace, i.e. on
