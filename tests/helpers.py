@@ -71,6 +71,10 @@ CHOLESKY_CASES = {
     "chol_f64_product_cap": ("product", False, 200, 50, 1e-9),       # stopped by the column cap
     "chol_f64c_product_240": ("product", True, 240, 240, 1e-5),     # 160 steps
     "chol_f64_last_column": ("product_full", False, 40, 40, 1e-14),  # full rank with K = N: the last column is counted
+    # rank 3 / rank 2 with a tolerance below the rounding noise: the stop comparison is taken on the noise that is left
+    "chol_f64_rank3_noise": ("lowrank3", False, 90, 90, 1e-14),
+    "chol_f64c_rank2_noise": ("lowrank2", True, 70, 70, 1e-14),
+    "chol_f64_rank3_noise_wide": ("lowrank3", False, 300, 300, 1e-15),
 }
 
 
@@ -84,11 +88,11 @@ def cholesky_case(name):
             G = G * np.array([1, 1j, -1, -1j])[(idx[:, None] - idx[None, :]) % 4]
         return G, cap, eps
     rng = np.random.default_rng(sum(map(ord, name)))
-    rows = n if kind == "product_full" else (2 * n) // 3
+    rows = n if kind == "product_full" else 3 if kind == "lowrank3" else 2 if kind == "lowrank2" else (2 * n) // 3
     B = rng.integers(-15, 16, size=(rows, n)).astype(np.float64)
     if cplx:
         B = B + 1j * rng.integers(-15, 16, size=(rows, n))
-    shift = np.zeros(rows) if kind == "product_full" else np.floor(14.0 * np.arange(rows) / rows)
+    shift = np.zeros(rows) if kind in ("product_full", "lowrank3", "lowrank2") else np.floor(14.0 * np.arange(rows) / rows)
     B = B * (2.0 ** -shift)[:, None]                                  # row weights 1 ... 2^-13: G spans 2^-26, exact
     return B.conj().T @ B, cap, eps
 
