@@ -136,9 +136,8 @@ class ClockSampler:
 
     def stop(self):
         t1 = time.time()
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
-            return out
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -146,18 +145,26 @@ class ClockSampler:
             self.proc.kill()
         self.file.flush()
         self.file.seek(0)
+        text = self.file.read()
+        os.unlink(self.file.name)
+        return self.summarise(text, self.t0, t1)
+
+    @classmethod
+    def summarise(cls, text, t0, t1):
+        """Median SM clock, maximum clock and the throttle reasons seen in the csv lines of `text` whose timestamp lies in
+        [t0, t1] (all lines if none does)."""
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         rows = []
-        for line in self.file.read().splitlines():
+        for line in text.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
                 continue
             try:
-                rows.append((self._stamp(parts[0]), float(parts[1]), float(parts[2]), parts[4:8]))
+                rows.append((cls._stamp(parts[0]), float(parts[1]), float(parts[2]), parts[4:8]))
             except ValueError:
                 continue
-        os.unlink(self.file.name)
-        inside = [r for r in rows if r[0] is not None and self.t0 - 0.02 <= r[0] <= t1 + 0.02]
+        inside = [r for r in rows if r[0] is not None and t0 - 0.02 <= r[0] <= t1 + 0.02]
         rows = inside or rows
         reasons = set()
         for _, _, _, flags in rows:

@@ -30,3 +30,24 @@ def test_stdout_guard_moves_library_output_to_stderr():
     code = ("import bench, os\nprint('first')\nwith bench.stdout_to_stderr():\n    os.write(1, b'banner\\n')\nprint('second')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=ROOT)
     assert r.returncode == 0 and r.stdout == "first\nsecond\n" and "banner" in r.stderr
+
+
+def test_clock_samples_are_cut_to_the_timed_region():
+    """ClockSampler.summarise keeps the nvidia-smi lines whose own timestamp lies inside the timed region and reports the
+    median clock and the throttle reasons of those lines only."""
+    import datetime
+    import bench
+    base = datetime.datetime(2026, 1, 2, 3, 4, 5).timestamp()
+
+    def line(offset, mhz, cap):
+        stamp = datetime.datetime.fromtimestamp(base + offset).strftime("%Y/%m/%d %H:%M:%S.%f")[:-3]
+        return f"{stamp}, {mhz}, 1965, 700.00, Not Active, Not Active, Not Active, {'Active' if cap else 'Not Active'}"
+
+    text = "\n".join([line(0.0, 1965, False), line(0.1, 1900, False), line(0.5, 1200, True), line(0.6, 1300, True), line(0.7, 1250, True),
+                      line(1.5, 1800, False), "garbage line"])
+    got = bench.ClockSampler.summarise(text, base + 0.45, base + 0.75)
+    assert got["samples"] == 3 and got["samples_inside_timed_region"] == 3
+    assert got["sm_mhz"] == 1250 and got["sm_max_mhz"] == 1965 and got["reasons"] == ["sw_power_cap"]
+    # a region too short to catch a line falls back to all lines
+    got = bench.ClockSampler.summarise(text, base + 0.31, base + 0.32)
+    assert got["samples"] == 6 and got["samples_inside_timed_region"] == 0
